@@ -1,0 +1,239 @@
+"""Known-answer tests that pin the CPU oracle to the reference's own unit tests.
+
+Every value below is the expectation of a test in the reference, re-expressed
+against the C restatement (file:line of the reference test is given per case).
+"""
+import math
+
+import numpy as np
+import pytest
+
+
+def test_e4m3_known_values(oracle):
+    # crates/weightstream-core/src/quant.rs:233-240
+    assert oracle.e4m3_to_f32(0x38) == 1.0
+    assert oracle.e4m3_to_f32(0xB8) == -1.0
+    assert oracle.e4m3_to_f32(0x7E) == 448.0
+    assert oracle.e4m3_to_f32(0x00) == 0.0
+    assert math.isnan(oracle.e4m3_to_f32(0x7F))
+    assert oracle.e4m3_to_f32(0x01) == 0.001953125
+
+
+def test_e8m0_is_power_of_two(oracle):
+    # crates/weightstream-core/src/quant.rs:243-248
+    assert oracle.e8m0_to_f32(127) == 1.0
+    assert oracle.e8m0_to_f32(126) == 0.5
+    assert oracle.e8m0_to_f32(137) == 1024.0
+    assert math.isnan(oracle.e8m0_to_f32(0xFF))
+
+
+def test_fp4_nibble_order(oracle):
+    # crates/weightstream-core/src/quant.rs:222-230: low nibble = even element
+    assert (oracle.fp4_to_f32(0x10 & 0xF), oracle.fp4_to_f32(0x10 >> 4)) == (0.0, 0.5)
+    assert (oracle.fp4_to_f32(0xF7 & 0xF), oracle.fp4_to_f32(0xF7 >> 4)) == (6.0, -6.0)
+
+
+def test_log2_ceil_and_pow2(oracle):
+    # crates/weightstream-core/src/quant.rs:259-269
+    assert oracle.log2_ceil(1.0) == 0
+    assert oracle.log2_ceil(0.99) == 0
+    assert oracle.log2_ceil(np.float32(1.0) / np.float32(448.0)) == -8
+    assert oracle.log2_ceil(1.0 / 512.0) == -9
+    assert oracle.log2_ceil(448.0) == 9
+    assert oracle.pow2i(-9) == 1.0 / 512.0
+    assert oracle.pow2i(9) == 512.0
+    assert oracle.ue8m0_round_scale(100.0, 448.0) == 0.25
+
+
+def test_bf16_roundtrip_and_rne(oracle):
+    # crates/weightstream-core/src/quant.rs:272-282
+    for v in [0.0, 1.0, -1.0, 0.5, 3.140625, -123.0, 1.0078125]:
+        assert oracle.bf16_to_f32(oracle.f32_to_bf16(v)) == v
+    assert oracle.f32_to_bf16(1.0 + 3.0 / 1024.0) == oracle.f32_to_bf16(1.0)
+    assert oracle.bf16_to_f32(oracle.f32_to_bf16(1.0 + 5.0 / 1024.0)) == 1.0 + 8.0 / 1024.0
+
+
+def test_e4m3_encode_roundtrip_and_ties(oracle):
+    # crates/weightstream-core/src/quant.rs:285-306
+    for b in range(0x7F):
+        v = oracle.e4m3_to_f32(b)
+        assert oracle.f32_to_e4m3(v) == b
+        assert oracle.f32_to_e4m3(-v) == (b | 0x80)
+    assert oracle.f32_to_e4m3(1000.0) == 0x7E
+    assert oracle.f32_to_e4m3(-1000.0) == 0xFE
+    assert oracle.f32_to_e4m3(448.0) == 0x7E
+    assert oracle.f32_to_e4m3(0.5 + 1.0 / 512.0) == 0x30
+    assert oracle.f32_to_e4m3(0.5 + 1.0 / 32.0) == 0x30
+    assert oracle.f32_to_e4m3(np.float32(0.5 + 1.0 / 32.0 + 1e-6)) == 0x31
+    assert oracle.f32_to_e4m3(1.5 / 512.0) == 0x02
+    assert oracle.f32_to_e4m3(2.5 / 512.0) == 0x02
+
+
+def test_e2m1_encode_ties(oracle):
+    # crates/weightstream-core/src/quant.rs:309-330
+    for code in range(16):
+        v = oracle.fp4_to_f32(code)
+        assert oracle.f32_to_e2m1(v) & 7 == code & 7
+        if v != 0.0:
+            assert oracle.f32_to_e2m1(v) == code
+    expect = {0.25: 0, 0.75: 2, 1.25: 2, 1.75: 4, 2.5: 4, 3.5: 6, 5.0: 6, 7.0: 7, -7.0: 0xF}
+    for v, c in expect.items():
+        assert oracle.f32_to_e2m1(v) == c
+    assert oracle.fp4_to_f32(oracle.f32_to_e2m1(-0.25)) == 0.0
+
+
+def test_fp8_snap_grid(oracle):
+    # crates/weightstream-ref/src/actquant.rs:181-200
+    x = np.zeros(32, dtype=np.float32)
+    x[:4] = [100.0, -100.0, 3.0, 0.001]
+    y = oracle.fp8_snap(x)
+    assert y[0] == 96.0 and y[1] == -96.0 and y[2] == 3.0
+    assert abs(y[3] - 0.0009765625) < 1e-9
+    assert np.all(y[4:] == 0.0)
+    assert np.all(oracle.fp8_snap(np.zeros(32, dtype=np.float32)) == 0.0)
+
+
+def test_fp8_act_emit_matches_snap(oracle):
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal(4096) * np.exp(rng.uniform(-12, 12, 4096))).astype(np.float32)
+    q, s = oracle.fp8_act_emit(x)
+    from weightstream_b200 import formats as F
+    deq = F.e4m3_to_f32(q) * np.repeat(F.e8m0_to_f32(s), 32)
+    assert np.array_equal(deq.view(np.uint32), oracle.fp8_snap(x).view(np.uint32))
+
+
+def test_fp8_gemv_matches_dense_dequant(oracle):
+    # crates/weightstream-ref/src/actquant.rs:226-252
+    rows = cols = 32
+    w = np.array([(i % 200) if (i % 200) != 0x7F else 0x7E for i in range(rows * cols)],
+                 dtype=np.uint8).reshape(rows, cols)
+    scales = np.full((1, 1), 127, dtype=np.uint8)
+    x = np.array([((i * np.float32(0.01)) - np.float32(0.15)) * np.float32(448.0) / np.float32(200.0)
+                  for i in range(cols)], dtype=np.float32)
+    y = oracle.fp8_gemv(w, scales, x, bn=32, bk=32)[0]
+    qa = oracle.fp8_snap(x)
+    for n in range(rows):
+        want = np.float32(0.0)
+        for c in range(cols):
+            want = np.float32(want + np.float32(qa[c] * np.float32(oracle.e4m3_to_f32(int(w[n, c])))))
+        assert abs(y[n] - want) < 1e-4
+
+
+def test_fp4_gemv_matches_dense_dequant(oracle):
+    # crates/weightstream-ref/src/actquant.rs:254-270 and quant.rs:346-356
+    rows, cols = 4, 64
+    w = np.array([i % 251 for i in range(rows * cols // 2)], dtype=np.uint8).reshape(rows, cols // 2)
+    scales = np.full((rows, cols // 32), 127, dtype=np.uint8)
+    x = np.array([(i * np.float32(0.02) - np.float32(0.6)) * np.float32(6.0) / np.float32(4.0)
+                  for i in range(cols)], dtype=np.float32)
+    y = oracle.fp4_gemv(w, scales, x)[0]
+    qa = oracle.fp8_snap(x)
+    from weightstream_b200 import formats as F
+    dense = F.dequant_fp4(w, scales)
+    for n in range(rows):
+        want = np.float32(0.0)
+        for c in range(cols):
+            want = np.float32(want + np.float32(dense[n, c] * qa[c]))
+        assert abs(y[n] - want) < 1e-4
+    d4 = F.dequant_fp4(np.full((2, 32), 0x12, dtype=np.uint8),
+                       np.array([[127, 128], [129, 130]], dtype=np.uint8))
+    assert (d4[0, 0], d4[0, 1], d4[0, 32], d4[1, 0], d4[1, 31]) == (1.0, 0.5, 2.0, 4.0, 2.0)
+
+
+def test_fp8_gemv_nonunit_scales(oracle):
+    # crates/weightstream-gpu/src/tests.rs:1813-1869: n=256, k=64, scales 120..124;
+    # the block-scaled result equals the dense dequantised dot within 1e-3.
+    rng = np.random.default_rng(78)
+    n, k = 256, 64
+    from weightstream_b200 import formats as F
+    a = F.e4m3_to_f32(F.f32_to_e4m3(((rng.uniform(0, 3, k) % 3.0) - 1.0) * 0.5))
+    wq = F.f32_to_e4m3(((rng.uniform(0, 3, (n, k)) % 3.0) - 1.0) * 0.25)
+    sb = np.array([120 + (i % 5) for i in range((n // 32) * (k // 32))], dtype=np.uint8).reshape(n // 32, k // 32)
+    y = oracle.fp8_gemv(wq, sb, a, bn=32, bk=32)[0]
+    dense = F.dequant_fp8(wq, sb, 32, 32).astype(np.float64)
+    want = dense @ oracle.fp8_snap(a).astype(np.float64)
+    assert np.max(np.abs(y - want)) < 1e-3
+
+
+def test_routing_weight_before_quant(oracle):
+    # crates/weightstream-ref/src/moe.rs:267-298: expert(1.5*w) != 1.5*expert(w) bitwise
+    rng = np.random.default_rng(31337)
+    n, k = 64, 64
+    from weightstream_b200 import formats as F
+    w2, s2 = F.quantize_fp4_rows(rng.uniform(-0.2, 0.2, (n, k)).astype(np.float32))
+    h = np.array([((i % 7) - 3.0) * 0.11 for i in range(k)], dtype=np.float32)
+    ids = np.array([[0]], dtype=np.int32)
+    a = oracle.moe_down_combine(w2[None], s2[None], 0, h[None], ids, np.array([[1.0]], np.float32))
+    b = oracle.moe_down_combine(w2[None], s2[None], 0, h[None], ids, np.array([[1.5]], np.float32))
+    assert not np.array_equal(b, np.float32(1.5) * a)
+    assert np.all(np.isfinite(b))
+
+
+def test_moe_ascending_id_order(oracle):
+    rng = np.random.default_rng(9)
+    n, k, E = 32, 64, 6
+    from weightstream_b200 import formats as F
+    ws, ss = zip(*[F.quantize_fp4_rows(rng.standard_normal((n, k)).astype(np.float32) * 50) for _ in range(E)])
+    w2, s2 = np.stack(ws), np.stack(ss)
+    ids = np.array([[5, 1, 3]], dtype=np.int32)
+    rw = np.array([[0.3, 0.5, 0.2]], dtype=np.float32)
+    h = rng.standard_normal((3, k)).astype(np.float32)
+    y = oracle.moe_down_combine(w2, s2, 0, h, ids, rw)[0]
+    parts = {int(ids[0, s]): oracle.fp4_gemv(w2[ids[0, s]], s2[ids[0, s]], h[s] * rw[0, s])[0] for s in range(3)}
+    want = np.zeros(n, dtype=np.float32)
+    for e in sorted(parts):
+        want = want + parts[e]
+    assert np.array_equal(y.view(np.uint32), want.view(np.uint32))
+    # an expert outside the local slab is skipped
+    y2 = oracle.moe_down_combine(w2[1:4], s2[1:4], 1, h, ids, rw)[0]
+    want2 = (np.zeros(n, dtype=np.float32) + parts[1]) + parts[3]
+    assert np.array_equal(y2.view(np.uint32), want2.view(np.uint32))
+
+
+def test_argmax_first_wins(oracle):
+    # crates/weightstream-ref/src/sample.rs:120-124 and crates/weightstream-cuda/src/gpu.rs:1372-1401
+    assert oracle.argmax(np.array([1, 3, 2], np.float32)) == 1
+    assert oracle.argmax(np.array([3, 3, 1], np.float32)) == 0
+    assert oracle.argmax(np.full(4, -np.inf, np.float32)) == 0
+    big = np.linspace(-1, 0, 129280).astype(np.float32)
+    big[500] = big[90000] = 7.0
+    assert oracle.argmax(big) == 500
+
+
+def test_rank_ordered_fold(oracle):
+    # crates/weightstream-transport/src/ring.rs:614-630: order changes bits
+    a = np.array([1.0, 1e20, -1e20, 1e-40], dtype=np.float32)
+    out = oracle.allreduce_fold(a.reshape(4, 1))
+    want = np.float32(np.float32(np.float32(a[0] + a[1]) + a[2]) + a[3])
+    assert out[0].view(np.uint32) == want.view(np.uint32)
+    swapped = oracle.allreduce_fold(a[[0, 2, 1, 3]].reshape(4, 1))
+    s2 = np.float32(np.float32(np.float32(a[0] + a[2]) + a[1]) + a[3])
+    assert swapped[0].view(np.uint32) == s2.view(np.uint32)
+    g = oracle.allgather(np.arange(8, dtype=np.float32).reshape(4, 2))
+    assert np.array_equal(g, np.arange(8, dtype=np.float32))
+
+
+def test_formats_match_oracle_encoders(oracle):
+    """The numpy input quantisers produce the oracle encoders' bytes."""
+    from weightstream_b200 import formats as F
+    rng = np.random.default_rng(3)
+    vals = (rng.standard_normal(20000) * np.exp(rng.uniform(-20, 8, 20000))).astype(np.float32)
+    special = np.array([0.0, -0.0, 448.0, 1000.0, -1000.0, 2.0 ** -6, 2.0 ** -9, 2.0 ** -10,
+                        1.5 / 512, 2.5 / 512, 7.5 / 512, 0.5 + 1 / 32, 464.0, 447.9], np.float32)
+    vals = np.concatenate([vals, special])
+    want = np.array([oracle.f32_to_e4m3(float(v)) for v in vals], dtype=np.uint8)
+    assert np.array_equal(F.f32_to_e4m3(vals), want)
+    v4 = np.concatenate([rng.uniform(-7, 7, 5000).astype(np.float32),
+                         np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25, 7, -7], np.float32)])
+    want4 = np.array([oracle.f32_to_e2m1(float(v)) for v in v4], dtype=np.uint8)
+    assert np.array_equal(F.f32_to_e2m1(v4), want4)
+    wantb = np.array([oracle.f32_to_bf16(float(v)) for v in vals], dtype=np.uint16)
+    assert np.array_equal(F.f32_to_bf16_bits(vals), wantb)
+    m = (rng.standard_normal((160, 384)) * 0.02).astype(np.float32)
+    for kind, name, bn, bk in [(1, "f32", 128, 128), (0, "ue8m0", 32, 32)]:
+        w0, s0 = oracle.encode_fp8(m, kind, bn, bk)
+        w1, s1 = F.quantize_fp8_blocks(m, bn, bk, name)
+        assert np.array_equal(w0, w1) and np.array_equal(s0.view(np.uint8), np.ascontiguousarray(s1).view(np.uint8))
+    w0, s0 = oracle.encode_fp4(m)
+    w1, s1 = F.quantize_fp4_rows(m)
+    assert np.array_equal(w0, w1) and np.array_equal(s0, s1)
