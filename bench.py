@@ -1,0 +1,315 @@
+#!/usr/bin/env python
+"""Benchmark of the fused tensor-parallel reduction step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one fused attention-output-projection step: the row-parallel FP8 GEMM
+(x bf16 [M, 8192/N] against this rank's K slice of W FP8 E4M3 [7168, 8192], 128x128 fp32
+block scales) together with the rank-ordered fp32 all-reduce, M = 1 (decode).  Work is
+fixed and K is split over the N GPUs (strong scaling).  Consecutive steps use different
+weight sets ("layers"), together several times larger than L2, so every step streams its
+weights from HBM.  The line printed on rank 0 carries the device-timed value, the
+end-to-end value through host buffers, the HBM roofline of the kernel, and the CPU
+baseline (the oracle port of the reference's single-threaded CPU path) timed beside it.
+
+With --impl reference the reference's CPU implementation of the same step (the oracle
+port, all host threads) is timed instead; nothing of the CUDA library is used.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_OUT, K_FULL = 7168, 8192
+BN = BK = 128
+METRIC = "us per fused GEMM+all-reduce step (o_proj, M=1)"
+
+
+def algorithmic_bytes(m: int, n: int, k_local: int) -> int:
+    """Distinct bytes one rank must move through HBM for one step: weights + block scales
+    + activations + reduced output (exchange slots excluded)."""
+    return n * k_local + (-(-n // BN)) * (k_local // BK) * 4 + m * k_local * 2 + m * n * 4
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(self.index),
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def make_cpu_inputs(seed: int, m: int):
+    """Host copy of one o_proj weight set for the CPU legs (numpy quantiser, same formats)."""
+    from weightstream_b200 import formats as F, synth
+    rng = np.random.default_rng(seed)
+    w, sc = synth.fp8_weight(rng, N_OUT, K_FULL)
+    x = F.bf16_bits_to_f32(synth.activations_bf16(rng, m, K_FULL))
+    return w, sc, x
+
+
+def time_oracle(threads: int, budget_s: float, m: int = 1):
+    """Time the oracle port of the reference's CPU path on the full o_proj step."""
+    from oracle import oracle as O
+    O.build()
+    w, sc, x = make_cpu_inputs(1234, m)
+    O.fp8_gemv(w[:256], sc, x, bn=BN, bk=BK, threads=threads)  # warm the library
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 200):
+        t0 = time.perf_counter()
+        O.fp8_gemv(w, sc, x, bn=BN, bk=BK, threads=threads)
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times) * 1e6, len(times)
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    O.build()
+    cores = O.max_threads()
+    w, sc, x = make_cpu_inputs(1234, 1)
+    step = lambda: O.fp8_gemv(w, sc, x, bn=BN, bk=BK, threads=cores)
+    for _ in range(max(1, min(args.warmup, 3))):
+        step()
+    steps = max(1, min(args.steps, 50))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    us = (time.perf_counter() - t0) / steps * 1e6
+    line = {
+        "impl": "reference", "metric": METRIC, "value": us, "unit": "us", "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32 accumulate over fp8 e4m3", "data": "synthetic",
+        "config": {"workload": "o_proj fp8 [7168x8192] + rank-ordered fold, M=1, whole K on the host"},
+        "cpu_baseline": {"value": us, "unit": "us", "cores": cores, "kind": "port",
+                         "sample": f"{steps} full steps, OpenMP over output rows (reference arithmetic, Rust original cannot be built here)"},
+        "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+    from weightstream_b200 import synth, tp
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    m = args.m
+    sh = tp.Sharding(world, rank)
+    k0, kl = sh.slice_of(K_FULL)
+    l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
+    per_set = N_OUT * kl
+    layers = max(4, int(np.ceil(3.0 * l2_bytes / per_set)))
+    layers = min(layers, 64)
+
+    ep = tp.Endpoint(sh, local_rank, max_m=max(m, 8), max_n=N_OUT, wait_ms=5000)
+    if world > 1:
+        ep.connect_process_group()
+
+    # every rank quantises the SAME full tensors (same seed) and keeps its K slice
+    ws, scs = [], []
+    for l in range(layers):
+        w, sc = synth.torch_fp8_weight(N_OUT, K_FULL, seed=synth.config_seed("o_proj", m, 1) + l, device=dev)
+        ws.append(w[:, k0:k0 + kl].contiguous())
+        scs.append(sc)
+        del w
+    g = torch.Generator(device=dev)
+    g.manual_seed(99)
+    x_full = torch.randn((m, K_FULL), generator=g, device=dev).to(torch.bfloat16)
+    x = x_full[:, k0:k0 + kl].contiguous()
+    outs = [torch.empty((m, N_OUT), dtype=torch.float32, device=dev) for _ in range(2)]
+
+    def step(i: int):
+        l = i % layers
+        ep.fp8_rowpar_gemm_allreduce(x, ws[l], scs[l], block=(BN, BK), k0=k0, out=outs[i & 1])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    ep.check()
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = ep.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ep.check()
+    ms_total = e0.elapsed_time(e1)
+    launches = ep.launches - launches0
+
+    # isolated steps: one event pair per step, device idle in between
+    iso = []
+    for i in range(min(args.steps, 50)):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record()
+        step(i)
+        b.record()
+        torch.cuda.synchronize()
+        iso.append(a.elapsed_time(b) * 1e3)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # end to end through host buffers: activations copied in, reduced rows copied out, every step
+    x_host = x.view(torch.int16).cpu().numpy().view(np.uint16)
+    e2e_steps = max(10, min(args.steps, 200))
+    for i in range(3):
+        ep.fp8_rowpar_gemm_allreduce_host(x_host, ws[i % layers], scs[i % layers], block=(BN, BK), k0=k0)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        ep.fp8_rowpar_gemm_allreduce_host(x_host, ws[i % layers], scs[i % layers], block=(BN, BK), k0=k0)
+    torch.cuda.synchronize()
+    e2e_us = (time.perf_counter() - t0) / e2e_steps * 1e6
+
+    vals = torch.tensor([ms_total, e2e_us, statistics.median(iso)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    ms_total, e2e_us, iso_us = [float(v) for v in vals.tolist()]
+    us_per_step = ms_total * 1e3 / args.steps
+
+    if rank == 0:
+        peak, peak_src = measured_peak_gbs()
+        abytes = algorithmic_bytes(m, N_OUT, kl)
+        achieved = abytes / (us_per_step * 1e-6) / 1e9
+        traffic = None
+        try:
+            with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+                traffic = json.load(f).get(f"fp8_rowpar_kernel_r{world}_m{m}")
+        except Exception:
+            pass
+        cpu_us, cpu_n = time_oracle(1, 12.0, m)
+        line = {
+            "metric": METRIC, "value": us_per_step, "unit": "us", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": us_per_step / 1e3, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8 e4m3 x fp8 e4m3 -> f32", "data": "synthetic",
+            "config": {"workload": f"o_proj fp8 [7168x8192] K/{world} per rank + fused fp32 all-reduce, M={m}",
+                       "m": m, "n": N_OUT, "k": K_FULL, "k_per_rank": kl, "parallelism": f"tp{world}",
+                       "l2": f"{layers} rotating weight sets ({layers * per_set / 1e6:.0f} MB per rank) > "
+                             f"{l2_bytes / 1e6:.0f} MB L2; no flush needed",
+                       "timing": "CUDA events around all steps back to back on one stream, max over ranks"},
+            "isolated_us": iso_us,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": traffic, "peak_source": f"of {peak_src}", "algorithmic_bytes": abytes,
+                         "frac_of_8TBs": achieved / 8000.0},
+            "cpu_baseline": {"value": cpu_us, "unit": "us", "cores": 1, "kind": "port",
+                             "sample": f"{cpu_n} full o_proj steps (M={m}, whole K), single thread as the reference engine runs"},
+            "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": int(m * kl * 2),
+                    "d2h_bytes_per_step": int(m * N_OUT * 4)},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    ep.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=1, help="activation rows per step (1 = decode)")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

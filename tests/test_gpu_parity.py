@@ -1,0 +1,421 @@
+"""GPU parity tests: the CUDA library, called through its C ABI, against the CPU oracle
+on the same seeded bytes.
+
+Bars: bit-exact for the activation quantiser, the bare collectives, argmax and the
+cross-rank agreement of every fused operator; relative L2 <= 1e-3 on fp32 outputs
+(the tolerance the path's specification states; observed values are ~1e-6).
+Multi-rank cases run as virtual ranks of one cooperative kernel on a single GPU.
+"""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+pytestmark = pytest.mark.gpu
+
+REL_L2_TOL = 1e-3
+
+
+def rel_l2(got: np.ndarray, want: np.ndarray) -> float:
+    d = np.linalg.norm(got.astype(np.float64) - want.astype(np.float64))
+    return float(d / max(np.linalg.norm(want.astype(np.float64)), 1e-30))
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.fail("a CUDA device is required for -m gpu tests")
+    torch.cuda.set_device(0)
+    return torch.device("cuda:0")
+
+
+@pytest.fixture(scope="module")
+def tpmod():
+    from weightstream_b200 import tp
+    return tp
+
+
+def bf16_tensor(bits: np.ndarray, dev):
+    return torch.from_numpy(bits.view(np.int16)).to(dev).view(torch.bfloat16)
+
+
+def u8(a: np.ndarray, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+# ----------------------------------------------------------------------------- act quant
+def test_act_quant_bit_exact_all_bf16(dev, tpmod, oracle):
+    """Every finite bf16 value, in blocks of mixed magnitudes: E4M3 bytes and UE8M0
+    exponents equal the oracle's (crates/weightstream-ref/src/actquant.rs:21-57)."""
+    from weightstream_b200 import formats as F
+    allbits = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    finite = allbits[(allbits & 0x7F80) != 0x7F80]
+    rng = np.random.default_rng(0)
+    rows = []
+    for _ in range(6):
+        rows.append(rng.permutation(finite)[: (finite.size // 32) * 32])
+    rows.append(np.sort(finite)[: (finite.size // 32) * 32])  # blocks of similar magnitude
+    bits = np.stack(rows)
+    x = bf16_tensor(bits, dev)
+    q, s = tpmod.act_quant_fp8(x)
+    torch.cuda.synchronize()
+    xf = F.bf16_bits_to_f32(bits)
+    for r in range(bits.shape[0]):
+        qo, so = oracle.fp8_act_emit(xf[r])
+        assert np.array_equal(q[r].cpu().numpy(), qo), f"row {r} bytes differ"
+        assert np.array_equal(s[r].cpu().numpy(), so), f"row {r} exponents differ"
+
+
+def test_act_quant_f32_edge_cases(dev, tpmod, oracle):
+    rng = np.random.default_rng(1)
+    x = (rng.standard_normal((4, 2048)) * np.exp(rng.uniform(-30, 30, (4, 2048)))).astype(np.float32)
+    x[0, :32] = 0.0
+    x[0, 32:64] = [100.0, -100.0, 3.0, 0.001] + [0.0] * 28       # actquant.rs:181-193
+    x[1, :4] = [448.0, -448.0, 464.0, 1e-4]
+    x[2, :3] = [np.inf, -np.inf, 1.0]
+    x[3, :2] = [3.0e38, -3.0e38]
+    q, s = tpmod.act_quant_fp8(torch.from_numpy(x).to(dev))
+    torch.cuda.synchronize()
+    for r in range(4):
+        qo, so = oracle.fp8_act_emit(x[r])
+        assert np.array_equal(q[r].cpu().numpy(), qo)
+        assert np.array_equal(s[r].cpu().numpy(), so)
+
+
+# ----------------------------------------------------------------------------- FP8 GEMM, TP=1
+FP8_CASES = [
+    # n, k, scale, bn, bk, ms
+    (256, 64, "ue8m0", 32, 32, (1, 3)),          # crates/weightstream-gpu/src/tests.rs:1818 shape
+    (96, 8192, "ue8m0", 32, 32, (3,)),           # crates/weightstream-cuda/src/gpu.rs:505 shape
+    (512, 1024, "f32", 128, 128, (1, 2, 8, 13)),
+    (5120, 2304, "ue8m0", 32, 32, (1,)),         # reference shared-expert w2 (docs/model-spec.md)
+    (7168, 2048, "f32", 128, 128, (1, 5)),       # shared-expert down at the measured shape
+]
+
+
+@pytest.mark.parametrize("n,k,scale,bn,bk,ms", FP8_CASES)
+@pytest.mark.parametrize("split", [True, False])
+def test_fp8_gemm_tp1(dev, tpmod, oracle, n, k, scale, bn, bk, ms, split):
+    from weightstream_b200 import formats as F, synth
+    rng = np.random.default_rng(synth.config_seed(f"fp8-{n}-{k}-{scale}", 0, 1))
+    w, sc = synth.fp8_weight(rng, n, k, scale=scale, bn=bn, bk=bk)
+    ep = tpmod.Endpoint(max_m=16, max_n=max(n, 16))
+    ep.set_split(split)
+    try:
+        wd, sd = u8(w, dev), torch.from_numpy(np.ascontiguousarray(sc)).to(dev)
+        for m in ms:
+            xb = synth.activations_bf16(rng, m, k)
+            out = ep.fp8_rowpar_gemm_allreduce(bf16_tensor(xb, dev), wd, sd, block=(bn, bk))
+            ep.check()
+            want = oracle.fp8_gemv(w, sc, F.bf16_bits_to_f32(xb), bn=bn, bk=bk, threads=oracle.max_threads())
+            err = rel_l2(out.cpu().numpy(), want)
+            assert err <= REL_L2_TOL, f"m={m}: rel L2 {err:.3e}"
+            assert err < 5e-5, f"m={m}: rel L2 {err:.3e} is within tolerance but far above summation noise"
+    finally:
+        ep.close()
+
+
+def test_fp8_gemm_f32_activations_and_strided_weight(dev, tpmod, oracle):
+    """fp32 activations (what the reference engine feeds, engine.rs:3988) and a weight that is
+    a column window of a wider matrix (row stride > k) with its k0 scale offset."""
+    from weightstream_b200 import synth
+    rng = np.random.default_rng(7)
+    n, kfull, k0, k = 256, 1024, 256, 512
+    w, sc = synth.fp8_weight(rng, n, kfull)
+    x = rng.standard_normal((2, k)).astype(np.float32)
+    ep = tpmod.Endpoint(max_m=8, max_n=n)
+    try:
+        wd = u8(w, dev)
+        out = ep.fp8_rowpar_gemm_allreduce(torch.from_numpy(x).to(dev), wd[:, k0:k0 + k],
+                                           torch.from_numpy(sc).to(dev), k0=k0)
+        ep.check()
+        want = oracle.fp8_gemv(w[:, k0:k0 + k], sc, x, bn=128, bk=128, k0=k0)
+        assert rel_l2(out.cpu().numpy(), want) < 5e-5
+    finally:
+        ep.close()
+
+
+def test_oproj_full_size_tp1(dev, tpmod, oracle):
+    """o_proj at the measured size: x bf16 [1, 8192], W FP8 [7168, 8192], 128x128 fp32 scales."""
+    from weightstream_b200 import formats as F, synth
+    rng = np.random.default_rng(synth.config_seed("o_proj", 1, 1))
+    n, k = 7168, 8192
+    w, sc = synth.fp8_weight(rng, n, k)
+    xb = synth.activations_bf16(rng, 1, k)
+    ep = tpmod.Endpoint(max_m=8, max_n=n)
+    try:
+        out = ep.fp8_rowpar_gemm_allreduce(bf16_tensor(xb, dev), u8(w, dev), torch.from_numpy(sc).to(dev))
+        ep.check()
+        want = oracle.fp8_gemv(w, sc, F.bf16_bits_to_f32(xb), bn=128, bk=128, threads=oracle.max_threads())
+        err = rel_l2(out.cpu().numpy(), want)
+        assert err <= REL_L2_TOL and err < 5e-5, err
+    finally:
+        ep.close()
+
+
+# ----------------------------------------------------------------------------- FP8 GEMM, TP>1
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("n,k,m", [(512, 2048, 1), (7168, 8192, 1), (7168, 8192, 5), (1024, 1024, 19)])
+def test_fp8_gemm_allreduce_virtual_ranks(dev, tpmod, oracle, world, n, k, m):
+    """K sharded over `world` ranks (engine.rs:1477-1480); partials added in rank order
+    (ring.rs:399-408); every rank must hold identical bits."""
+    from weightstream_b200 import formats as F, synth
+    if k // world % 128:
+        pytest.skip("slice not aligned to the scale block")
+    rng = np.random.default_rng(synth.config_seed("o_proj", m, world))
+    w, sc = synth.fp8_weight(rng, n, k)
+    xb = synth.activations_bf16(rng, m, k)
+    xf = F.bf16_bits_to_f32(xb)
+    grp = tpmod.LocalGroup(world, max_m=32, max_n=n)
+    try:
+        wd, sd, xd = u8(w, dev), torch.from_numpy(sc).to(dev), bf16_tensor(xb, dev)
+        xs, ws, k0s, parts = [], [], [], []
+        for r in range(world):
+            k0, kl = tpmod.Sharding(world, r).slice_of(k)
+            xs.append(xd[:, k0:k0 + kl])
+            ws.append(tpmod.shard_weight(wd, (n, k), tpmod.WShard.Cols(k0, kl)))
+            k0s.append(k0)
+            parts.append(oracle.fp8_gemv(w[:, k0:k0 + kl], sc, xf[:, k0:k0 + kl], bn=128, bk=128, k0=k0,
+                                         threads=oracle.max_threads()))
+        outs = grp.fp8_rowpar_gemm_allreduce(xs, ws, [sd] * world, k0s=k0s)
+        grp.check()
+        want = oracle.allreduce_fold(np.stack(parts))
+        got = [o.cpu().numpy() for o in outs]
+        for r in range(1, world):
+            assert np.array_equal(got[0].view(np.uint32), got[r].view(np.uint32)), f"rank {r} differs from rank 0"
+        err = rel_l2(got[0], want)
+        assert err <= REL_L2_TOL and err < 5e-5, err
+    finally:
+        grp.close()
+
+
+# ----------------------------------------------------------------------------- collectives
+def gate_vector(rnd: int, rank: int, n: int, world: int) -> np.ndarray:
+    """Per-rank distinct values with extremes that never overflow the rank-ordered sum, in the
+    spirit of crates/weightstream-transport/src/bench.rs:135-171."""
+    rng = np.random.default_rng(rnd * 1000 + rank)
+    v = np.empty(n, dtype=np.float32)
+    kind = rng.integers(0, 6, n)
+    mant = rng.integers(0, 1 << 23, n).astype(np.uint32)
+    v[:] = (rng.integers(0, 1001, n) - 500).astype(np.float32)
+    v[kind == 0] = (mant[kind == 0] % 0x00800000).view(np.float32)                   # subnormal or zero
+    v[kind == 1] = (np.uint32(0x6E000000) | mant[kind == 1]).view(np.float32)        # ~2^93
+    v[kind == 2] = -(np.uint32(0x6E000000) | mant[kind == 2]).view(np.float32)
+    v[kind == 3] = (np.uint32(0x3F800000) | mant[kind == 3]).view(np.float32)        # [1, 2)
+    carrier = rank == rnd % world
+    v[0] = np.finfo(np.float32).max if carrier else np.float32(1e-40)
+    v[1] = -np.finfo(np.float32).max if carrier else np.float32(1e-40)
+    v[2] = np.uint32(1).view(np.float32) if carrier else 0.0
+    return v
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_collectives_bit_exact(dev, tpmod, oracle, world):
+    n = 7168
+    grp = tpmod.LocalGroup(world, max_m=1, max_n=n)
+    try:
+        for rnd in range(4):  # crosses both banks twice
+            ins = [gate_vector(rnd, r, n, world) for r in range(world)]
+            dins = [torch.from_numpy(v).to(dev) for v in ins]
+            red = grp.allreduce(dins)
+            gat = grp.allgather(dins)
+            grp.check()
+            want = oracle.allreduce_fold(np.stack(ins))
+            for r in range(world):
+                assert np.array_equal(red[r].cpu().numpy().view(np.uint32), want.view(np.uint32))
+                assert np.array_equal(gat[r].cpu().numpy().view(np.uint32), np.concatenate(ins).view(np.uint32))
+    finally:
+        grp.close()
+
+
+def test_collectives_trait_tp1(dev, tpmod):
+    """Collectives::allreduce / ::allgather on a world of one: host slice in, host vector out."""
+    ep = tpmod.Endpoint(max_m=1, max_n=1024)
+    try:
+        c = tpmod.Collectives(ep)
+        v = np.arange(1000, dtype=np.float32) * 0.5
+        assert np.array_equal(c.allreduce(v), v)
+        assert np.array_equal(c.allgather(v), v)
+        with pytest.raises(tpmod.WsError):
+            c.allreduce(np.zeros(2000, np.float32))  # longer than the endpoint was sized for
+        assert "collectives=2" in c.stats()
+    finally:
+        ep.close()
+
+
+def test_wait_times_out_and_context_survives(dev, tpmod):
+    """Fail-stop (ring.rs:439-458): a rank whose peer never takes the step gives up after
+    wait_ms, the kernel returns, the host sees WS_ERR_TIMEOUT and the device stays usable."""
+    grp = tpmod.LocalGroup(2, max_m=1, max_n=256, wait_ms=20)
+    try:
+        v = torch.ones(256, device=dev)
+        out = torch.empty_like(v)
+        ep0 = grp.eps[0]
+        ep0._ok(ep0.lib.ws_allreduce_f32(ep0.handle, v.data_ptr(), out.data_ptr(), 256, tpmod._stream_ptr()))
+        with pytest.raises(tpmod.WsError) as ei:
+            ep0.check()
+        assert ei.value.status == tpmod._lib.WS_ERR_TIMEOUT
+        assert float((v + 1).sum().item()) == 512.0  # the context still works
+    finally:
+        grp.close()
+
+
+# ----------------------------------------------------------------------------- lm_head
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("m", [1, 3])
+def test_lm_head_small_vs_oracle(dev, tpmod, oracle, world, m):
+    """Vocab-sharded head whose shards cut a 128-row scale block (as 129280/8 does): logits equal
+    the oracle's, argmax equals sample.rs:13-23 on the oracle's logits."""
+    from weightstream_b200 import formats as F, synth
+    vocab, k = 8 * 2064, 1024          # 2064 = 16*129: shards of 2064 rows are not multiples of 128
+    rng = np.random.default_rng(synth.config_seed("lm_head_small", m, world))
+    w, sc = synth.fp8_weight(rng, vocab, k)
+    xb = synth.activations_bf16(rng, m, k)
+    xf = F.bf16_bits_to_f32(xb)
+    want = oracle.fp8_gemv(w, sc, xf, bn=128, bk=128, threads=oracle.max_threads())
+    grp = tpmod.LocalGroup(world, max_m=8, max_n=16, max_vocab=vocab)
+    try:
+        wd, sd, xd = u8(w, dev), torch.from_numpy(sc).to(dev), bf16_tensor(xb, dev)
+        ws, scs, row0s, v0s = [], [], [], []
+        for r in range(world):
+            v0, vl = tpmod.Sharding(world, r).slice_of(vocab)
+            ws.append(tpmod.shard_weight(wd, (vocab, k), tpmod.WShard.Rows(v0, vl), align=16))
+            s_r, row0, _ = tpmod.shard_scale(sd, sd.shape, tpmod.WShard.Rows(v0, vl), block=(128, 128))
+            scs.append(s_r.contiguous())
+            row0s.append(row0)
+            v0s.append(v0)
+        logits, amax = grp.lm_head_allgather_argmax([xd] * world, ws, scs, vocab=vocab, vocab_row0s=v0s, row0s=row0s)
+        grp.check()
+        for r in range(world):
+            got = logits[r].cpu().numpy()
+            assert rel_l2(got, want) < 5e-5
+            assert np.array_equal(got.view(np.uint32), logits[0].cpu().numpy().view(np.uint32))
+            for t in range(m):
+                assert int(amax[r][t].item()) == oracle.argmax(want[t]) == oracle.argmax(got[t])
+        # argmax-only fast path (no logits gather) gives the same indices
+        _, amax2 = grp.lm_head_allgather_argmax([xd] * world, ws, scs, vocab=vocab, vocab_row0s=v0s, row0s=row0s,
+                                                want_logits=False)
+        grp.check()
+        assert torch.equal(amax2[0], amax[0])
+    finally:
+        grp.close()
+
+
+def test_lm_head_argmax_ties_lowest_index(dev, tpmod, oracle):
+    """Two identical weight rows give equal maxima; the lower index must win
+    (crates/weightstream-cuda/src/gpu.rs:1372-1401 places them at 500 and 90000)."""
+    from weightstream_b200 import formats as F, synth
+    vocab, k = 129280 // 8 * 2, 256
+    rng = np.random.default_rng(11)
+    w, sc = synth.fp8_weight(rng, vocab, k)
+    xb = synth.activations_bf16(rng, 1, k)
+    xq = oracle.fp8_snap(F.bf16_bits_to_f32(xb)[0])
+    # a row perfectly aligned with x maximises the logit; plant it twice inside one scale block
+    best = F.f32_to_e4m3(np.sign(xq) * 448.0)
+    lo, hi = 500, 500 + 64
+    w[lo] = best
+    w[hi] = best
+    world = 2
+    grp = tpmod.LocalGroup(world, max_m=1, max_n=16, max_vocab=vocab)
+    try:
+        wd, sd, xd = u8(w, dev), torch.from_numpy(sc).to(dev), bf16_tensor(xb, dev)
+        ws, scs, row0s, v0s = [], [], [], []
+        for r in range(world):
+            v0, vl = tpmod.Sharding(world, r).slice_of(vocab)
+            ws.append(wd[v0:v0 + vl])
+            s_r, row0, _ = tpmod.shard_scale(sd, sd.shape, tpmod.WShard.Rows(v0, vl), block=(128, 128))
+            scs.append(s_r.contiguous()); row0s.append(row0); v0s.append(v0)
+        logits, amax = grp.lm_head_allgather_argmax([xd] * world, ws, scs, vocab=vocab, vocab_row0s=v0s, row0s=row0s)
+        grp.check()
+        l0 = logits[0].cpu().numpy()[0]
+        assert l0[lo] == l0[hi] == l0.max()
+        assert int(amax[0][0].item()) == lo == oracle.argmax(l0)
+        assert int(amax[1][0].item()) == lo
+    finally:
+        grp.close()
+
+
+# ----------------------------------------------------------------------------- MoE down + combine
+def moe_case(rng, m, n_experts, top_k, n, k):
+    from weightstream_b200 import formats as F, synth
+    w2, s2 = synth.fp4_experts(rng, n_experts, n, k)
+    ids, rw = synth.routes(rng, m, n_experts, top_k)
+    hb = F.f32_to_bf16_bits(rng.standard_normal((m * top_k, k)).astype(np.float32))
+    return w2, s2, ids, rw, hb
+
+
+@pytest.mark.parametrize("m,n_experts,top_k,n,k", [
+    (1, 16, 6, 256, 512),
+    (5, 16, 6, 512, 256),
+    (64, 32, 6, 7168, 256),       # several routes per expert, some with more than 8
+    (1, 8, 6, 7168, 2048),        # one token at the measured expert shape
+    (3, 8, 2, 5120, 2304),        # reference-native expert shape
+])
+@pytest.mark.parametrize("split", [True, False])
+def test_moe_down_combine_tp1(dev, tpmod, oracle, m, n_experts, top_k, n, k, split):
+    from weightstream_b200 import formats as F
+    rng = np.random.default_rng(1000 + m + n + k)
+    w2, s2, ids, rw, hb = moe_case(rng, m, n_experts, top_k, n, k)
+    ep = tpmod.Endpoint(max_m=64, max_n=n)
+    ep.set_split(split)
+    try:
+        out = ep.moe_down_combine_allreduce(bf16_tensor(hb, dev), torch.from_numpy(ids).to(dev),
+                                            torch.from_numpy(rw).to(dev), u8(w2, dev), u8(s2, dev), 0)
+        ep.check()
+        want = oracle.moe_down_combine(w2, s2, 0, F.bf16_bits_to_f32(hb), ids, rw, threads=oracle.max_threads())
+        err = rel_l2(out.cpu().numpy(), want)
+        assert err <= REL_L2_TOL and err < 5e-5, err
+    finally:
+        ep.close()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("m", [1, 8, 64])
+def test_moe_down_combine_virtual_ranks(dev, tpmod, oracle, world, m):
+    """Experts sharded by id (engine.rs:1194-1195); rank partials (local ascending-id sums) added
+    in rank order; identical bits on all ranks.  Some ranks own no selected expert at m=1."""
+    from weightstream_b200 import formats as F
+    n_experts, top_k, n, k = 32, 6, 1024, 512
+    rng = np.random.default_rng(2000 + m + world)
+    w2, s2, ids, rw, hb = moe_case(rng, m, n_experts, top_k, n, k)
+    hf = F.bf16_bits_to_f32(hb)
+    grp = tpmod.LocalGroup(world, max_m=64, max_n=n)
+    try:
+        hd, idd, rwd = bf16_tensor(hb, dev), torch.from_numpy(ids).to(dev), torch.from_numpy(rw).to(dev)
+        w2d, s2d = u8(w2, dev), u8(s2, dev)
+        parts, w2s, s2s, e0s = [], [], [], []
+        for r in range(world):
+            e0, el = tpmod.Sharding(world, r).slice_of(n_experts)
+            w2s.append(w2d[e0:e0 + el]); s2s.append(s2d[e0:e0 + el]); e0s.append(e0)
+            parts.append(oracle.moe_down_combine(w2[e0:e0 + el], s2[e0:e0 + el], e0, hf, ids, rw,
+                                                 threads=oracle.max_threads()))
+        outs = grp.moe_down_combine_allreduce([hd] * world, [idd] * world, [rwd] * world, w2s, s2s, e0s)
+        grp.check()
+        want = oracle.allreduce_fold(np.stack(parts))
+        got = [o.cpu().numpy() for o in outs]
+        for r in range(1, world):
+            assert np.array_equal(got[0].view(np.uint32), got[r].view(np.uint32))
+        err = rel_l2(got[0], want)
+        assert err <= REL_L2_TOL and err < 5e-5, err
+    finally:
+        grp.close()
+
+
+def test_routing_weight_is_applied_before_quantisation(dev, tpmod):
+    """crates/weightstream-ref/src/moe.rs:267-298: expert(1.5*w) differs bitwise from 1.5*expert(w)."""
+    from weightstream_b200 import formats as F, synth
+    rng = np.random.default_rng(31337)
+    n, k = 256, 256
+    w2, s2 = synth.fp4_experts(rng, 1, n, k, std=0.2)
+    h = np.array([((i % 7) - 3.0) * 0.11 for i in range(k)], dtype=np.float32)[None]
+    ids = torch.zeros((1, 1), dtype=torch.int32, device=dev)
+    ep = tpmod.Endpoint(max_m=1, max_n=n)
+    try:
+        hd = torch.from_numpy(h).to(dev)
+        a = ep.moe_down_combine_allreduce(hd, ids, torch.tensor([[1.0]], device=dev), u8(w2, dev), u8(s2, dev), 0)
+        b = ep.moe_down_combine_allreduce(hd, ids, torch.tensor([[1.5]], device=dev), u8(w2, dev), u8(s2, dev), 0)
+        ep.check()
+        assert not torch.equal(b, 1.5 * a)
+        assert torch.isfinite(b).all()
+    finally:
+        ep.close()

@@ -1,0 +1,704 @@
+// Host side of the C ABI declared in include/ws_tp.h: endpoint life cycle, peer
+// mapping, argument validation, tensor-map construction and kernel launches.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/ws_tp.h"
+#include "ws_device.cuh"
+#include "ws_fp8_kernel.cuh"
+#include "ws_misc_kernels.cuh"
+#include "ws_moe_kernel.cuh"
+
+using namespace ws;
+
+struct ws_tp {
+    int world = 1, rank = 0, device = 0;
+    ws_tp_config_t cfg{};
+    SymLayout lay{};
+    char *sym = nullptr;                 // this rank's exchange region
+    char *peers[WS_MAX_WORLD] = {};      // every rank's region as mapped in this process
+    bool opened[WS_MAX_WORLD] = {};      // mapped through an IPC handle (must be closed)
+    bool connected = false;
+    float *contrib = nullptr;
+    uint32_t *counters = nullptr;
+    uint32_t *status = nullptr;
+    uint64_t step = 0, launches = 0;
+    int sm_count = 0, ncta = 0;
+    uint64_t timeout_ns = 0;
+    int split = 1;
+    // host-buffer entry points
+    cudaStream_t hstream = nullptr;
+    void *pin = nullptr;
+    size_t pin_bytes = 0;
+    void *dev_stage = nullptr;
+    size_t dev_stage_bytes = 0;
+    std::string err;
+};
+
+namespace {
+
+constexpr int kSmemBudget = 227 * 1024 - 1024;  // opt-in maximum minus alignment slack
+
+ws_status_t fail(ws_tp *tp, ws_status_t code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (tp) tp->err = buf;
+    return code;
+}
+
+#define WS_CUDA(tp, call)                                                                   \
+    do {                                                                                    \
+        cudaError_t e_ = (call);                                                            \
+        if (e_ != cudaSuccess)                                                              \
+            return fail(tp, WS_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_));   \
+    } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// Row-major byte matrix [rows][row_bytes] with stride `ld` bytes, 128 x 16 boxes, 128B swizzle.
+ws_status_t make_tmap(ws_tp *tp, CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes,
+                      uint64_t ld) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(tp, WS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld & 15))
+        return fail(tp, WS_ERR_INVALID, "weight base and row stride must be multiples of 16 bytes");
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint64_t strides[1] = {ld};
+    cuuint32_t box[2] = {128, (cuuint32_t)kGroupRows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(tp, WS_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return WS_OK;
+}
+
+RankCtx make_ctx(const ws_tp *tp) {
+    RankCtx c{};
+    for (int i = 0; i < WS_MAX_WORLD; ++i) c.sym[i] = tp->peers[i];
+    c.contrib = tp->contrib;
+    c.counters = tp->counters;
+    c.status = tp->status;
+    c.rank = tp->rank;
+    return c;
+}
+
+template <typename K>
+ws_status_t set_smem(ws_tp *tp, K kernel) {
+    WS_CUDA(tp, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    return WS_OK;
+}
+
+template <typename P>
+ws_status_t launch(ws_tp *tp, void (*kernel)(P), const P &params, int ncta, int nvr, int threads, size_t smem,
+                   cudaStream_t stream) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)ncta, (unsigned)nvr, 1);
+    cfg.blockDim = dim3((unsigned)threads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    // Virtual ranks sharing one device wait on one another inside the kernel: they must be
+    // co-resident, which a cooperative launch guarantees (or refuses).
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = nvr > 1 ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    WS_CUDA(tp, cudaLaunchKernelEx(&cfg, kernel, params));
+    tp->launches++;
+    return WS_OK;
+}
+
+// Common checks for a group call; returns the CTA count to use.
+ws_status_t group_prelude(ws_tp *const *ranks, int n, int *ncta, bool *same_device) {
+    if (!ranks || n < 1 || n > WS_MAX_WORLD) return WS_ERR_INVALID;
+    ws_tp *t0 = ranks[0];
+    if (!t0) return WS_ERR_INVALID;
+    bool same = true;
+    for (int i = 0; i < n; ++i) {
+        ws_tp *t = ranks[i];
+        if (!t) return fail(t0, WS_ERR_INVALID, "null endpoint %d", i);
+        if (t->world > 1 && !t->connected) return fail(t0, WS_ERR_INVALID, "endpoint %d is not connected", i);
+        if (t->step != t0->step) return fail(t0, WS_ERR_SEQUENCE, "endpoints disagree on the step count");
+        if (t->device != t0->device) same = false;
+    }
+    if (n > 1) {
+        if (n != t0->world) return fail(t0, WS_ERR_INVALID, "a group call needs all %d ranks", t0->world);
+        for (int i = 0; i < n; ++i)
+            if (ranks[i]->rank != i) return fail(t0, WS_ERR_INVALID, "ranks[] must be ordered by rank");
+    }
+    if (!same)  // kernels that wait on one another must not be separate launches on one GPU
+        for (int i = 0; i < n; ++i)
+            for (int j = i + 1; j < n; ++j)
+                if (ranks[i]->device == ranks[j]->device)
+                    return fail(t0, WS_ERR_UNSUPPORTED, "ranks %d and %d share device %d while others do not", i, j,
+                                ranks[i]->device);
+    int c = t0->ncta;
+    if (n > 1 && same) c = std::min(c, t0->sm_count / n);
+    if (c < 1) return fail(t0, WS_ERR_CAPACITY, "no CTAs left per virtual rank");
+    *ncta = c;
+    *same_device = same;
+    return WS_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------
+extern "C" {
+
+const char *ws_version(void) { return "weightstream_b200 0.1 (sm_100a)"; }
+
+ws_status_t ws_tp_create(int32_t world, int32_t rank, int32_t device, const ws_tp_config_t *cfg, ws_tp_t **out) {
+    if (!out || !cfg) return WS_ERR_INVALID;
+    *out = nullptr;
+    if (!(world == 1 || world == 2 || world == 4 || world == 8) || rank < 0 || rank >= world) return WS_ERR_INVALID;
+    if (cfg->max_m < 1 || cfg->max_n < 16 || cfg->max_vocab < 0) return WS_ERR_INVALID;
+    ws_tp *tp = new ws_tp();
+    tp->world = world;
+    tp->rank = rank;
+    tp->device = device;
+    tp->cfg = *cfg;
+    tp->timeout_ns = (uint64_t)(cfg->wait_ms > 0 ? cfg->wait_ms : 2000) * 1000000ull;
+    auto bail = [&](ws_status_t s) {
+        ws_tp_destroy(tp);
+        return s;
+    };
+    if (cudaSetDevice(device) != cudaSuccess) return bail(WS_ERR_CUDA);
+    if (cudaDeviceGetAttribute(&tp->sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+        return bail(WS_ERR_CUDA);
+    tp->ncta = cfg->num_ctas > 0 ? std::min(cfg->num_ctas, tp->sm_count) : tp->sm_count;
+    if (tp->ncta > kMaxCtas) tp->ncta = kMaxCtas;
+    tp->lay = make_layout(world, cfg->max_m, cfg->max_n, cfg->max_vocab);
+    if (cudaMalloc(&tp->sym, (size_t)tp->lay.total) != cudaSuccess) return bail(WS_ERR_CUDA);
+    if (cudaMemset(tp->sym, 0, (size_t)tp->lay.total) != cudaSuccess) return bail(WS_ERR_CUDA);
+    const size_t contrib_bytes = (size_t)kMaxCtas * kMaxRuns * 8 * kGroupRows * sizeof(float);
+    if (cudaMalloc(&tp->contrib, contrib_bytes) != cudaSuccess) return bail(WS_ERR_CUDA);
+    if (cudaMalloc(&tp->counters, (kMaxShared + 8) * sizeof(uint32_t)) != cudaSuccess) return bail(WS_ERR_CUDA);
+    if (cudaMemset(tp->counters, 0, (kMaxShared + 8) * sizeof(uint32_t)) != cudaSuccess) return bail(WS_ERR_CUDA);
+    tp->status = tp->counters + kMaxShared;
+    if (cudaStreamCreateWithFlags(&tp->hstream, cudaStreamNonBlocking) != cudaSuccess) return bail(WS_ERR_CUDA);
+    if (cudaDeviceSynchronize() != cudaSuccess) return bail(WS_ERR_CUDA);
+    tp->peers[rank] = tp->sym;
+    if (world == 1) tp->connected = true;
+    if (set_smem(tp, fp8_rowpar_kernel) != WS_OK || set_smem(tp, moe_down_kernel) != WS_OK) return bail(WS_ERR_CUDA);
+    *out = tp;
+    return WS_OK;
+}
+
+ws_status_t ws_tp_destroy(ws_tp_t *tp) {
+    if (!tp) return WS_OK;
+    cudaSetDevice(tp->device);
+    for (int i = 0; i < WS_MAX_WORLD; ++i)
+        if (tp->opened[i] && tp->peers[i]) cudaIpcCloseMemHandle(tp->peers[i]);
+    if (tp->hstream) cudaStreamDestroy(tp->hstream);
+    if (tp->pin) cudaFreeHost(tp->pin);
+    if (tp->dev_stage) cudaFree(tp->dev_stage);
+    if (tp->sym) cudaFree(tp->sym);
+    if (tp->contrib) cudaFree(tp->contrib);
+    if (tp->counters) cudaFree(tp->counters);
+    delete tp;
+    return WS_OK;
+}
+
+ws_status_t ws_tp_export_handle(ws_tp_t *tp, ws_ipc_handle_t *out) {
+    if (!tp || !out) return WS_ERR_INVALID;
+    static_assert(sizeof(cudaIpcMemHandle_t) + 16 <= WS_IPC_HANDLE_BYTES, "handle does not fit");
+    memset(out, 0, sizeof *out);
+    WS_CUDA(tp, cudaSetDevice(tp->device));
+    cudaIpcMemHandle_t h;
+    WS_CUDA(tp, cudaIpcGetMemHandle(&h, tp->sym));
+    memcpy(out->bytes, &h, sizeof h);
+    int64_t total = tp->lay.total;
+    int32_t meta[2] = {tp->world, tp->rank};
+    memcpy(out->bytes + sizeof h, &total, 8);
+    memcpy(out->bytes + sizeof h + 8, meta, 8);
+    return WS_OK;
+}
+
+ws_status_t ws_tp_connect_ipc(ws_tp_t *tp, const ws_ipc_handle_t *handles, int32_t n) {
+    if (!tp || !handles || n != tp->world) return WS_ERR_INVALID;
+    WS_CUDA(tp, cudaSetDevice(tp->device));
+    for (int r = 0; r < n; ++r) {
+        cudaIpcMemHandle_t h;
+        int64_t total;
+        int32_t meta[2];
+        memcpy(&h, handles[r].bytes, sizeof h);
+        memcpy(&total, handles[r].bytes + sizeof h, 8);
+        memcpy(meta, handles[r].bytes + sizeof h + 8, 8);
+        if (total != tp->lay.total || meta[0] != tp->world || meta[1] != r)
+            return fail(tp, WS_ERR_INVALID, "handle %d describes a different group (world/rank/layout)", r);
+        if (r == tp->rank) continue;
+        void *p = nullptr;
+        WS_CUDA(tp, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        tp->peers[r] = static_cast<char *>(p);
+        tp->opened[r] = true;
+    }
+    tp->connected = true;
+    return WS_OK;
+}
+
+ws_status_t ws_tp_connect_local(ws_tp_t *const *ranks, int32_t n) {
+    if (!ranks || n < 1 || n > WS_MAX_WORLD) return WS_ERR_INVALID;
+    for (int i = 0; i < n; ++i)
+        if (!ranks[i] || ranks[i]->world != n || ranks[i]->rank != i || ranks[i]->lay.total != ranks[0]->lay.total)
+            return fail(ranks[0], WS_ERR_INVALID, "ranks[] must hold the n endpoints of one group, ordered by rank");
+    for (int i = 0; i < n; ++i) {
+        ws_tp *a = ranks[i];
+        WS_CUDA(a, cudaSetDevice(a->device));
+        for (int j = 0; j < n; ++j) {
+            ws_tp *b = ranks[j];
+            if (a->device != b->device) {
+                int can = 0;
+                WS_CUDA(a, cudaDeviceCanAccessPeer(&can, a->device, b->device));
+                if (!can) return fail(a, WS_ERR_UNSUPPORTED, "device %d cannot map device %d", a->device, b->device);
+                cudaError_t e = cudaDeviceEnablePeerAccess(b->device, 0);
+                if (e == cudaErrorPeerAccessAlreadyEnabled) (void)cudaGetLastError();
+                else if (e != cudaSuccess) return fail(a, WS_ERR_CUDA, "cudaDeviceEnablePeerAccess: %s", cudaGetErrorString(e));
+            }
+            a->peers[j] = b->sym;
+        }
+        a->connected = true;
+    }
+    return WS_OK;
+}
+
+ws_status_t ws_tp_check(ws_tp_t *tp, void *stream) {
+    if (!tp) return WS_ERR_INVALID;
+    WS_CUDA(tp, cudaSetDevice(tp->device));
+    WS_CUDA(tp, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    uint32_t st = 0;
+    WS_CUDA(tp, cudaMemcpy(&st, tp->status, 4, cudaMemcpyDeviceToHost));
+    if (st == 0) return WS_OK;
+    WS_CUDA(tp, cudaMemset(tp->status, 0, 4));
+    const uint32_t where = st >> 24;
+    const char *what = where == 1   ? "a peer CTA's partial"
+                       : where == 2 ? "a peer's split-group partial"
+                       : where == 3 ? "a weight tile (TMA)"
+                       : where == 4 ? "the gather of every rank"
+                                    : "an unknown event";
+    return fail(tp, -(ws_status_t)(st & 0xFFu), "rank %d: wait for %s timed out after %llu ms; fail-stop, results invalid",
+                tp->rank, what, (unsigned long long)(tp->timeout_ns / 1000000ull));
+}
+
+const char *ws_tp_last_error(ws_tp_t *tp) { return tp ? tp->err.c_str() : "null endpoint"; }
+
+ws_status_t ws_tp_stats(ws_tp_t *tp, uint64_t *steps, uint64_t *launches) {
+    if (!tp) return WS_ERR_INVALID;
+    if (steps) *steps = tp->step;
+    if (launches) *launches = tp->launches;
+    return WS_OK;
+}
+
+int32_t ws_tp_num_ctas(ws_tp_t *tp) { return tp ? tp->ncta : 0; }
+
+// ------------------------------------------------------------------------------ FP8 GEMM
+static ws_status_t validate_fp8(ws_tp *tp, const ws_fp8_gemm_args_t &a, bool lm_head) {
+    if (!a.x || !a.w || !a.scales) return fail(tp, WS_ERR_INVALID, "null x / w / scales");
+    if (a.m < 1 || a.n < 16 || a.k < 32) return fail(tp, WS_ERR_INVALID, "bad shape m=%d n=%d k=%d", a.m, a.n, a.k);
+    if (a.k % 32) return fail(tp, WS_ERR_INVALID, "k=%d is not a multiple of the 32-wide activation block", a.k);
+    if (a.n % 16) return fail(tp, WS_ERR_INVALID, "n=%d is not a multiple of 16", a.n);
+    if (a.x_dtype != WS_ACT_BF16 && a.x_dtype != WS_ACT_F32) return fail(tp, WS_ERR_INVALID, "bad x_dtype");
+    const int xa = a.x_dtype == WS_ACT_BF16 ? 8 : 4;
+    if ((reinterpret_cast<uintptr_t>(a.x) & 15) || (a.ldx % xa) || a.ldx < a.k)
+        return fail(tp, WS_ERR_INVALID, "x must be 16-byte aligned with ldx >= k and ldx a multiple of %d", xa);
+    if (a.scale_kind != WS_SCALE_UE8M0 && a.scale_kind != WS_SCALE_F32) return fail(tp, WS_ERR_INVALID, "bad scale_kind");
+    if (a.block_n < 16 || a.block_n % 16 || a.block_k < 32 || a.block_k % 32)
+        return fail(tp, WS_ERR_INVALID, "scale block %dx%d: block_n must be a multiple of 16, block_k of 32", a.block_n, a.block_k);
+    if (a.row0 < 0 || a.k0 < 0 || a.row0 % 16) return fail(tp, WS_ERR_INVALID, "row0 must be a non-negative multiple of 16");
+    if ((a.k0 + a.k - 1) / a.block_k >= a.scale_ld) return fail(tp, WS_ERR_INVALID, "k slice reaches past scale_ld");
+    if (a.ldw < a.k) return fail(tp, WS_ERR_INVALID, "ldw < k");
+    if (!lm_head && !a.out) return fail(tp, WS_ERR_INVALID, "null out");
+    if (a.k > 32768) return fail(tp, WS_ERR_CAPACITY, "k=%d exceeds the decode kernel's shared-memory plan", a.k);
+    return WS_OK;
+}
+
+// One fused step over at most 8 activation rows.
+static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t *args, const ws_lm_head_args_t *lm,
+                            int m0, int mt, void *const *streams, int ncta, bool same_device) {
+    ws_tp *t0 = ranks[0];
+    const ws_fp8_gemm_args_t &a0 = lm ? lm[0].g : args[0];
+    Fp8Params p{};
+    p.m = mt; p.n = a0.n; p.k = a0.k; p.x_dtype = a0.x_dtype; p.scale_kind = a0.scale_kind;
+    p.bn = a0.block_n; p.bk = a0.block_k; p.world = t0->world;
+    p.mode = lm ? kModeLmHead : kModeAllReduce;
+    p.vocab = lm ? lm[0].vocab : 0;
+    p.gather_logits = 0;
+    p.mp = mt <= 1 ? 1 : mt <= 2 ? 2 : mt <= 4 ? 4 : 8;
+    p.split = t0->split;
+    p.timeout_ns = t0->timeout_ns;
+    p.lay = t0->lay;
+    const int kbox = (p.k + 127) / 128;
+    const int G = p.n / kGroupRows, Gm = G / ncta, Rg = G - Gm * ncta;
+    int64_t skb = 1;
+    for (int i = 0; i < n; ++i) {
+        const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
+        skb = std::max<int64_t>(skb, (a.k0 + a.k - 1) / a.block_k - a.k0 / a.block_k + 1);
+        if (lm && lm[i].logits) p.gather_logits = 1;
+    }
+    p.skb = (int)skb;
+    p.nslot_max = (Gm * kGroupRows) / p.bn + 2 + 1 + 4;
+    const int owned_rows = (Gm + ((!p.split && Rg) ? 1 : 0)) * kGroupRows;
+    if (p.split && Rg) {
+        const int64_t U = (int64_t)Rg * kbox;
+        const int64_t per = (U + ncta - 1) / ncta;
+        if ((per + kbox - 1) / kbox + 1 > 4) p.split = 0;  // would need more scale slots than planned
+    }
+    const Fp8Smem fixed = fp8_smem_layout(0, kbox, p.mp, p.nslot_max, p.skb, p.m, owned_rows);
+    int ns = (kSmemBudget - fixed.total) / kStageBytes;
+    if (ns > kMaxStages) ns = kMaxStages;
+    if (ns < 2) return fail(t0, WS_ERR_CAPACITY, "shapes m=%d n=%d k=%d leave no room for the weight stage ring", p.m, p.n, p.k);
+    p.nstages = ns;
+    const size_t smem = (size_t)fp8_smem_layout(ns, kbox, p.mp, p.nslot_max, p.skb, p.m, owned_rows).total + 1024;
+
+    for (int i = 0; i < n; ++i) {
+        ws_tp *t = ranks[i];
+        const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
+        Fp8RankArgs &r = p.r[i];
+        ws_status_t s = make_tmap(t, &r.tmap, a.w, (uint64_t)a.n, (uint64_t)a.k, (uint64_t)a.ldw);
+        if (s != WS_OK) { t0->err = t->err; return s; }
+        const size_t xes = a.x_dtype == WS_ACT_BF16 ? 2 : 4;
+        r.x = static_cast<const char *>(a.x) + (size_t)m0 * a.ldx * xes;
+        r.scales = a.scales;
+        r.out = lm ? nullptr : a.out + (size_t)m0 * a.n;
+        r.logits = lm && lm[i].logits ? lm[i].logits + (size_t)m0 * lm[i].vocab : nullptr;
+        r.argmax = lm && lm[i].argmax ? lm[i].argmax + m0 : nullptr;
+        r.ldx = a.ldx; r.scale_ld = a.scale_ld; r.row0 = a.row0; r.k0 = a.k0;
+        r.vocab_row0 = lm ? lm[i].vocab_row0 : 0;
+        r.ctx = make_ctx(t);
+    }
+    // every endpoint advances by one step
+    for (int i = 0; i < n; ++i) ranks[i]->step++;
+    p.seq = (uint32_t)t0->step;
+    if (same_device) {
+        WS_CUDA(t0, cudaSetDevice(t0->device));
+        return launch(t0, fp8_rowpar_kernel, p, ncta, n, kThreads, smem, static_cast<cudaStream_t>(streams ? streams[0] : nullptr));
+    }
+    for (int i = 0; i < n; ++i) {  // one launch per device, each sees itself as virtual rank 0
+        Fp8Params q = p;
+        q.r[0] = p.r[i];
+        WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
+        ws_status_t s = launch(ranks[i], fp8_rowpar_kernel, q, ncta, 1, kThreads, smem,
+                               static_cast<cudaStream_t>(streams ? streams[i] : nullptr));
+        if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
+    }
+    return WS_OK;
+}
+
+ws_status_t ws_fp8_rowpar_gemm_allreduce_group(ws_tp_t *const *ranks, int32_t n, const ws_fp8_gemm_args_t *args,
+                                               void *const *streams) {
+    int ncta;
+    bool same;
+    ws_status_t s = group_prelude(ranks, n, &ncta, &same);
+    if (s != WS_OK) return s;
+    ws_tp *t0 = ranks[0];
+    if (!args) return fail(t0, WS_ERR_INVALID, "null args");
+    for (int i = 0; i < n; ++i) {
+        s = validate_fp8(t0, args[i], false);
+        if (s != WS_OK) return s;
+        if (args[i].m != args[0].m || args[i].n != args[0].n || args[i].k != args[0].k ||
+            args[i].block_n != args[0].block_n || args[i].block_k != args[0].block_k ||
+            args[i].scale_kind != args[0].scale_kind || args[i].x_dtype != args[0].x_dtype)
+            return fail(t0, WS_ERR_INVALID, "ranks must pass equal shapes and formats");
+    }
+    if (args[0].m > t0->cfg.max_m || args[0].n > t0->cfg.max_n)
+        return fail(t0, WS_ERR_CAPACITY, "m=%d n=%d exceed the endpoint's max_m=%d max_n=%d", args[0].m, args[0].n,
+                    t0->cfg.max_m, t0->cfg.max_n);
+    for (int m0 = 0; m0 < args[0].m; m0 += 8) {
+        s = fp8_step(ranks, n, args, nullptr, m0, std::min(8, args[0].m - m0), streams, ncta, same);
+        if (s != WS_OK) return s;
+    }
+    return WS_OK;
+}
+
+ws_status_t ws_fp8_rowpar_gemm_allreduce(ws_tp_t *tp, const ws_fp8_gemm_args_t *args, void *stream) {
+    ws_tp_t *r[1] = {tp};
+    void *s[1] = {stream};
+    return ws_fp8_rowpar_gemm_allreduce_group(r, 1, args, s);
+}
+
+ws_status_t ws_lm_head_allgather_argmax_group(ws_tp_t *const *ranks, int32_t n, const ws_lm_head_args_t *args,
+                                              void *const *streams) {
+    int ncta;
+    bool same;
+    ws_status_t s = group_prelude(ranks, n, &ncta, &same);
+    if (s != WS_OK) return s;
+    ws_tp *t0 = ranks[0];
+    if (!args) return fail(t0, WS_ERR_INVALID, "null args");
+    bool any_logits = false;
+    for (int i = 0; i < n; ++i) {
+        s = validate_fp8(t0, args[i].g, true);
+        if (s != WS_OK) return s;
+        const ws_fp8_gemm_args_t &g = args[i].g, &g0 = args[0].g;
+        if (g.m != g0.m || g.n != g0.n || g.k != g0.k || g.block_n != g0.block_n || g.block_k != g0.block_k ||
+            g.scale_kind != g0.scale_kind || g.x_dtype != g0.x_dtype || args[i].vocab != args[0].vocab)
+            return fail(t0, WS_ERR_INVALID, "ranks must pass equal shapes and formats");
+        if (args[i].vocab_row0 < 0 || args[i].vocab_row0 + g.n > args[i].vocab)
+            return fail(t0, WS_ERR_INVALID, "vocab shard [%lld, +%d) lies outside vocab %d",
+                        (long long)args[i].vocab_row0, g.n, args[i].vocab);
+        any_logits |= args[i].logits != nullptr;
+    }
+    if (args[0].g.m > t0->cfg.max_m) return fail(t0, WS_ERR_CAPACITY, "m=%d exceeds max_m=%d", args[0].g.m, t0->cfg.max_m);
+    if (any_logits && args[0].vocab > t0->cfg.max_vocab)
+        return fail(t0, WS_ERR_CAPACITY, "vocab=%d exceeds the endpoint's max_vocab=%d", args[0].vocab, t0->cfg.max_vocab);
+    for (int m0 = 0; m0 < args[0].g.m; m0 += 8) {
+        s = fp8_step(ranks, n, nullptr, args, m0, std::min(8, args[0].g.m - m0), streams, ncta, same);
+        if (s != WS_OK) return s;
+    }
+    return WS_OK;
+}
+
+ws_status_t ws_lm_head_allgather_argmax(ws_tp_t *tp, const ws_lm_head_args_t *args, void *stream) {
+    ws_tp_t *r[1] = {tp};
+    void *s[1] = {stream};
+    return ws_lm_head_allgather_argmax_group(r, 1, args, s);
+}
+
+// ------------------------------------------------------------------------------ MoE down
+ws_status_t ws_moe_down_combine_allreduce_group(ws_tp_t *const *ranks, int32_t n, const ws_moe_down_args_t *args,
+                                                void *const *streams) {
+    int ncta;
+    bool same;
+    ws_status_t s = group_prelude(ranks, n, &ncta, &same);
+    if (s != WS_OK) return s;
+    ws_tp *t0 = ranks[0];
+    if (!args) return fail(t0, WS_ERR_INVALID, "null args");
+    const ws_moe_down_args_t &a0 = args[0];
+    for (int i = 0; i < n; ++i) {
+        const ws_moe_down_args_t &a = args[i];
+        if (!a.h || !a.route_ids || !a.route_w || !a.w2 || !a.s2 || !a.out) return fail(t0, WS_ERR_INVALID, "null argument");
+        if (a.m < 1 || a.top_k < 1 || a.top_k > kMoeMaxTopK || a.m * a.top_k > kMoeMaxRoutes)
+            return fail(t0, WS_ERR_CAPACITY, "m*top_k = %d*%d exceeds %d routes per step", a.m, a.top_k, kMoeMaxRoutes);
+        if (a.n % 16 || a.k % 256 || a.k < 256) return fail(t0, WS_ERR_INVALID, "n must be a multiple of 16 and k of 256");
+        if (a.e_len < 1 || a.e_len > kMoeMaxExperts || a.e_start < 0) return fail(t0, WS_ERR_INVALID, "bad local expert range");
+        if ((int64_t)a.e_len * a.n >= (1ll << 31)) return fail(t0, WS_ERR_CAPACITY, "expert slab has too many rows");
+        const int ha = a.h_dtype == WS_ACT_BF16 ? 8 : 4;
+        if ((reinterpret_cast<uintptr_t>(a.h) & 15) || (a.ldh % ha) || a.ldh < a.k)
+            return fail(t0, WS_ERR_INVALID, "h must be 16-byte aligned with ldh >= k and ldh a multiple of %d", ha);
+        if (reinterpret_cast<uintptr_t>(a.s2) & 15) return fail(t0, WS_ERR_INVALID, "s2 must be 16-byte aligned");
+        if (a.m != a0.m || a.n != a0.n || a.k != a0.k || a.top_k != a0.top_k || a.h_dtype != a0.h_dtype)
+            return fail(t0, WS_ERR_INVALID, "ranks must pass equal shapes and formats");
+    }
+    if (a0.m > t0->cfg.max_m || a0.n > t0->cfg.max_n)
+        return fail(t0, WS_ERR_CAPACITY, "m=%d n=%d exceed the endpoint's max_m=%d max_n=%d", a0.m, a0.n, t0->cfg.max_m, t0->cfg.max_n);
+
+    MoeParams p{};
+    p.m = a0.m; p.n = a0.n; p.k = a0.k; p.top_k = a0.top_k; p.h_dtype = a0.h_dtype; p.world = t0->world;
+    p.timeout_ns = t0->timeout_ns;
+    p.lay = t0->lay;
+    const int kbox = (p.k / 2 + 127) / 128;
+    p.stage_boxes = std::min(kbox, kBoxesPerStage);
+    const int G = p.n / kGroupRows, Gm = G / ncta, Rg = G - Gm * ncta;
+    p.split = t0->split;
+    // the split schedule gives one CTA at most ceil(Rg*routes/ncta)+1 (group, pass) runs
+    if (p.split && ((int64_t)Rg * p.m * p.top_k + ncta - 1) / ncta + 2 > kMaxRuns) p.split = 0;
+    const int owned_rows = (Gm + ((!p.split && Rg) ? 1 : 0)) * kGroupRows;
+    int e_len_max = 0;
+    for (int i = 0; i < n; ++i) e_len_max = std::max(e_len_max, args[i].e_len);
+    const MoeSmem fixed = moe_smem_layout(0, p.stage_boxes, p.k, p.m, p.top_k, e_len_max, owned_rows);
+    int ns = (kSmemBudget - fixed.total) / fixed.stage_bytes;
+    if (ns > kMaxStages) ns = kMaxStages;
+    if (ns < 2 || ns * fixed.stage_bytes < p.m * p.top_k * kGroupRows * 4)
+        return fail(t0, WS_ERR_CAPACITY, "shapes m=%d n=%d k=%d leave no room for the weight stage ring", p.m, p.n, p.k);
+    p.nstages = ns;
+    const size_t smem = (size_t)moe_smem_layout(ns, p.stage_boxes, p.k, p.m, p.top_k, e_len_max, owned_rows).total + 1024;
+    for (int i = 0; i < n; ++i) {
+        const ws_moe_down_args_t &a = args[i];
+        MoeRankArgs &r = p.r[i];
+        s = make_tmap(ranks[i], &r.tmap, a.w2, (uint64_t)a.e_len * a.n, (uint64_t)a.k / 2, (uint64_t)a.k / 2);
+        if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
+        r.h = a.h; r.route_ids = a.route_ids; r.route_w = a.route_w; r.s2 = a.s2; r.out = a.out;
+        r.ldh = a.ldh; r.e_start = a.e_start; r.e_len = e_len_max == a.e_len ? a.e_len : a.e_len;
+        r.ctx = make_ctx(ranks[i]);
+        if (a.e_len != e_len_max) return fail(t0, WS_ERR_INVALID, "ranks must hold equally many experts");
+    }
+    for (int i = 0; i < n; ++i) ranks[i]->step++;
+    p.seq = (uint32_t)t0->step;
+    if (same) {
+        WS_CUDA(t0, cudaSetDevice(t0->device));
+        return launch(t0, moe_down_kernel, p, ncta, n, kThreads, smem, static_cast<cudaStream_t>(streams ? streams[0] : nullptr));
+    }
+    for (int i = 0; i < n; ++i) {
+        MoeParams q = p;
+        q.r[0] = p.r[i];
+        WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
+        s = launch(ranks[i], moe_down_kernel, q, ncta, 1, kThreads, smem, static_cast<cudaStream_t>(streams ? streams[i] : nullptr));
+        if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
+    }
+    return WS_OK;
+}
+
+ws_status_t ws_moe_down_combine_allreduce(ws_tp_t *tp, const ws_moe_down_args_t *args, void *stream) {
+    ws_tp_t *r[1] = {tp};
+    void *s[1] = {stream};
+    return ws_moe_down_combine_allreduce_group(r, 1, args, s);
+}
+
+// ------------------------------------------------------------------------------ collectives
+static ws_status_t coll_group(ws_tp_t *const *ranks, int n, const float *const *in, float *const *out, int64_t len,
+                              void *const *streams, int gather) {
+    int ncta;
+    bool same;
+    ws_status_t s = group_prelude(ranks, n, &ncta, &same);
+    if (s != WS_OK) return s;
+    ws_tp *t0 = ranks[0];
+    if (!in || !out || len < 1) return fail(t0, WS_ERR_INVALID, "collective input len %lld not in 1..", (long long)len);
+    if (len > (int64_t)t0->cfg.max_m * t0->cfg.max_n)
+        return fail(t0, WS_ERR_CAPACITY, "collective input len %lld not in 1..=%lld", (long long)len,
+                    (long long)t0->cfg.max_m * t0->cfg.max_n);
+    CollParams p{};
+    p.len = len; p.world = t0->world; p.gather = gather; p.timeout_ns = t0->timeout_ns; p.lay = t0->lay;
+    for (int i = 0; i < n; ++i) {
+        if (!in[i] || !out[i]) return fail(t0, WS_ERR_INVALID, "null buffer");
+        p.r[i].in = in[i];
+        p.r[i].out = out[i];
+        p.r[i].ctx = make_ctx(ranks[i]);
+    }
+    ncta = (int)std::min<int64_t>(ncta, std::max<int64_t>(1, len / 256));
+    for (int i = 0; i < n; ++i) ranks[i]->step++;
+    p.seq = (uint32_t)t0->step;
+    if (same) {
+        WS_CUDA(t0, cudaSetDevice(t0->device));
+        return launch(t0, coll_kernel, p, ncta, n, 256, 0, static_cast<cudaStream_t>(streams ? streams[0] : nullptr));
+    }
+    for (int i = 0; i < n; ++i) {
+        CollParams q = p;
+        q.r[0] = p.r[i];
+        WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
+        s = launch(ranks[i], coll_kernel, q, ncta, 1, 256, 0, static_cast<cudaStream_t>(streams ? streams[i] : nullptr));
+        if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
+    }
+    return WS_OK;
+}
+
+ws_status_t ws_allreduce_f32_group(ws_tp_t *const *ranks, int32_t n, const float *const *in, float *const *out,
+                                   int64_t len, void *const *streams) {
+    return coll_group(ranks, n, in, out, len, streams, 0);
+}
+ws_status_t ws_allgather_f32_group(ws_tp_t *const *ranks, int32_t n, const float *const *in, float *const *out,
+                                   int64_t len, void *const *streams) {
+    return coll_group(ranks, n, in, out, len, streams, 1);
+}
+ws_status_t ws_allreduce_f32(ws_tp_t *tp, const float *in, float *out, int64_t len, void *stream) {
+    ws_tp_t *r[1] = {tp};
+    void *s[1] = {stream};
+    const float *i[1] = {in};
+    float *o[1] = {out};
+    return coll_group(r, 1, i, o, len, s, 0);
+}
+ws_status_t ws_allgather_f32(ws_tp_t *tp, const float *in, float *out, int64_t len, void *stream) {
+    ws_tp_t *r[1] = {tp};
+    void *s[1] = {stream};
+    const float *i[1] = {in};
+    float *o[1] = {out};
+    return coll_group(r, 1, i, o, len, s, 1);
+}
+
+// ------------------------------------------------------------------------------ host-buffer forms
+static ws_status_t ensure_staging(ws_tp *tp, size_t pin_bytes, size_t dev_bytes) {
+    WS_CUDA(tp, cudaSetDevice(tp->device));
+    if (pin_bytes > tp->pin_bytes) {
+        if (tp->pin) cudaFreeHost(tp->pin);
+        tp->pin = nullptr;
+        tp->pin_bytes = 0;
+        WS_CUDA(tp, cudaHostAlloc(&tp->pin, pin_bytes, cudaHostAllocDefault));
+        tp->pin_bytes = pin_bytes;
+    }
+    if (dev_bytes > tp->dev_stage_bytes) {
+        if (tp->dev_stage) cudaFree(tp->dev_stage);
+        tp->dev_stage = nullptr;
+        tp->dev_stage_bytes = 0;
+        WS_CUDA(tp, cudaMalloc(&tp->dev_stage, dev_bytes));
+        tp->dev_stage_bytes = dev_bytes;
+    }
+    return WS_OK;
+}
+
+static ws_status_t coll_host(ws_tp *tp, const float *in, float *out, int64_t len, int gather) {
+    if (!tp || !in || !out || len < 1) return WS_ERR_INVALID;
+    const size_t ib = (size_t)len * 4, ob = gather ? ib * tp->world : ib;
+    ws_status_t s = ensure_staging(tp, ib + ob, ib + ob);
+    if (s != WS_OK) return s;
+    char *pin = static_cast<char *>(tp->pin), *dev = static_cast<char *>(tp->dev_stage);
+    memcpy(pin, in, ib);
+    WS_CUDA(tp, cudaMemcpyAsync(dev, pin, ib, cudaMemcpyHostToDevice, tp->hstream));
+    s = gather ? ws_allgather_f32(tp, reinterpret_cast<float *>(dev), reinterpret_cast<float *>(dev + ib), len, tp->hstream)
+               : ws_allreduce_f32(tp, reinterpret_cast<float *>(dev), reinterpret_cast<float *>(dev + ib), len, tp->hstream);
+    if (s != WS_OK) return s;
+    WS_CUDA(tp, cudaMemcpyAsync(pin + ib, dev + ib, ob, cudaMemcpyDeviceToHost, tp->hstream));
+    s = ws_tp_check(tp, tp->hstream);
+    if (s != WS_OK) return s;
+    memcpy(out, pin + ib, ob);
+    return WS_OK;
+}
+ws_status_t ws_allreduce_f32_host(ws_tp_t *tp, const float *in, float *out, int64_t len) { return coll_host(tp, in, out, len, 0); }
+ws_status_t ws_allgather_f32_host(ws_tp_t *tp, const float *in, float *out, int64_t len) { return coll_host(tp, in, out, len, 1); }
+
+ws_status_t ws_fp8_rowpar_gemm_allreduce_host(ws_tp_t *tp, const ws_fp8_gemm_args_t *dw, const void *x_host, float *out_host) {
+    if (!tp || !dw || !x_host || !out_host) return WS_ERR_INVALID;
+    const size_t es = dw->x_dtype == WS_ACT_BF16 ? 2 : 4;
+    const size_t xb = (size_t)dw->m * dw->k * es, xb_al = (xb + 255) / 256 * 256, ob = (size_t)dw->m * dw->n * 4;
+    ws_status_t s = ensure_staging(tp, xb_al + ob, xb_al + ob);
+    if (s != WS_OK) return s;
+    char *pin = static_cast<char *>(tp->pin), *dev = static_cast<char *>(tp->dev_stage);
+    memcpy(pin, x_host, xb);
+    WS_CUDA(tp, cudaMemcpyAsync(dev, pin, xb, cudaMemcpyHostToDevice, tp->hstream));
+    ws_fp8_gemm_args_t a = *dw;
+    a.x = dev;
+    a.ldx = dw->k;
+    a.out = reinterpret_cast<float *>(dev + xb_al);
+    s = ws_fp8_rowpar_gemm_allreduce(tp, &a, tp->hstream);
+    if (s != WS_OK) return s;
+    WS_CUDA(tp, cudaMemcpyAsync(pin + xb_al, dev + xb_al, ob, cudaMemcpyDeviceToHost, tp->hstream));
+    s = ws_tp_check(tp, tp->hstream);
+    if (s != WS_OK) return s;
+    memcpy(out_host, pin + xb_al, ob);
+    return WS_OK;
+}
+
+// ------------------------------------------------------------------------------ act quant
+ws_status_t ws_act_quant_fp8(const void *x, int64_t ldx, int32_t x_dtype, int32_t m, int32_t k, uint8_t *q,
+                             uint8_t *sexp, void *stream) {
+    if (!x || !q || !sexp || m < 1 || k < 32 || k % 32) return WS_ERR_INVALID;
+    const int xa = x_dtype == WS_ACT_BF16 ? 8 : 4;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7) || ldx % xa || ldx < k) return WS_ERR_INVALID;
+    const int64_t total = (int64_t)m * (k / 8);
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    act_quant_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, ldx, x_dtype, m, k, q, sexp);
+    return cudaGetLastError() == cudaSuccess ? WS_OK : WS_ERR_CUDA;
+}
+
+// Testing knob: 0 makes the leftover row groups whole-CTA work instead of K-split work.
+ws_status_t ws_tp_set_split(ws_tp_t *tp, int32_t on) {
+    if (!tp) return WS_ERR_INVALID;
+    tp->split = on ? 1 : 0;
+    return WS_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,255 @@
+// Device-side building blocks shared by the sm_100a kernels: PTX wrappers
+// (mbarrier, TMA tile loads, ldmatrix, FP8 tensor-core MMA, system-scope flags),
+// the bit-exact activation quantiser and the exchange layout.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ws_tp.h"
+
+namespace ws {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;  // + one TMA producer warp
+constexpr int kBoxBytes = 2048;                  // one TMA box: 16 rows x 128 bytes
+constexpr int kBoxesPerStage = 16;
+constexpr int kStageBytes = kBoxBytes * kBoxesPerStage;  // 32 KB
+constexpr int kMaxStages = 6;
+constexpr int kMaxCtas = 160;    // persistent CTAs per rank (one per SM on B200: 148)
+constexpr int kMaxShared = 160;  // output row groups whose K range is split across CTAs
+constexpr int kMaxRuns = 16;     // split contributions one CTA may produce
+constexpr int kGroupRows = 16;   // MMA M: output rows per group
+
+// Error detail codes written to the device status word (high byte) with WS_ERR_*.
+enum : uint32_t {
+    kStatOk = 0,
+    kStatTimeoutPeerA = 0x01000000u,  // waiting for a peer CTA's owned-rows flag
+    kStatTimeoutPeerB = 0x02000000u,  // waiting for a peer's split-group flag
+    kStatTimeoutTma = 0x03000000u,    // a weight tile never landed in shared memory
+    kStatTimeoutGather = 0x04000000u
+};
+
+// ---------------------------------------------------------------- exchange layout
+// Every rank allocates one region with this layout; peers map it and store into it.
+struct SymLayout {
+    int64_t flags_off;   // u32  [2 banks][R src][kMaxCtas + kMaxShared]
+    int64_t pairs_off;   // u64  [2][R][kMaxCtas][max_m]      (argmax candidates)
+    int64_t slotb_off;   // f32  [2][R][kMaxShared][8*16... sized max_m*16]
+    int64_t slota_off;   // f32  [2][R][max_m*max_n]
+    int64_t gather_off;  // f32  [2][max_m*max_vocab]
+    int64_t total;
+    int32_t max_m, max_n, max_vocab, world;
+};
+
+__host__ __device__ inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+__host__ inline SymLayout make_layout(int world, int max_m, int max_n, int max_vocab) {
+    SymLayout L{};
+    L.world = world; L.max_m = max_m; L.max_n = max_n; L.max_vocab = max_vocab;
+    int64_t o = 0;
+    L.flags_off = o;  o += align_up((int64_t)2 * world * (kMaxCtas + kMaxShared) * 4, 256);
+    L.pairs_off = o;  o += align_up((int64_t)2 * world * kMaxCtas * max_m * 8, 256);
+    L.slotb_off = o;  o += align_up((int64_t)2 * world * kMaxShared * max_m * kGroupRows * 4, 256);
+    L.slota_off = o;  o += align_up((int64_t)2 * world * max_m * max_n * 4, 256);
+    L.gather_off = o; o += align_up((int64_t)2 * max_m * (int64_t)max_vocab * 4, 256);
+    L.total = o;
+    return L;
+}
+
+// What one (possibly virtual) rank needs inside a kernel to reach its group.
+struct RankCtx {
+    char *sym[WS_MAX_WORLD];  // sym[p] = rank p's exchange region as mapped here
+    float *contrib;           // local: [kMaxCtas][kMaxRuns][8*16] split contributions
+    uint32_t *counters;       // local: [kMaxShared] arrival counters (self-resetting)
+    uint32_t *status;         // local: first error wins
+    int32_t rank;
+    int32_t pad;
+};
+
+// ---------------------------------------------------------------- small PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~2^27 probes (seconds), records why, and lets the
+// caller unwind instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *status) {
+    for (uint32_t i = 0; i < (1u << 27); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    atomicCAS(status, 0u, kStatTimeoutTma | (uint32_t)(-WS_ERR_TIMEOUT));
+    return false;
+}
+
+// 2-D TMA tile load global -> shared, completion on an mbarrier (no multicast).
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int32_t x,
+                                            int32_t y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1,
+                                            uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t &r0, uint32_t &r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+                 : "=r"(r0), "=r"(r1)
+                 : "r"(addr));
+}
+
+// D(16x8, f32) = A(16x32 e4m3, row) * B(32x8 e4m3, col); accumulator starts at zero.
+__device__ __forceinline__ void mma_e4m3_16x8x32(float (&d)[4], uint32_t a0, uint32_t a1,
+                                                 uint32_t a2, uint32_t a3, uint32_t b0,
+                                                 uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+__device__ __forceinline__ void consumer_bar() {  // the 8 consumer warps only
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+
+// ---------------------------------------------------------------- system-scope flags
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_volatile_f32(const float *p) {
+    float v;
+    asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint64_t ld_volatile_u64(const uint64_t *p) {
+    uint64_t v;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Poll `flag` until it carries `seq`.  Every wait is bounded by `timeout_ns`: on
+// expiry the first error is recorded in *status and the caller returns normally
+// (fail-stop at the host, never a trap or an endless spin).
+__device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t seq, uint64_t timeout_ns,
+                                          uint32_t *status, uint32_t code) {
+    if (ld_acquire_sys(flag) == seq) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        for (int i = 0; i < 32; ++i) {
+            if (ld_acquire_sys(flag) == seq) return true;
+        }
+        if (globaltimer_ns() - t0 > timeout_ns) {
+            atomicCAS(status, 0u, code | (uint32_t)(-WS_ERR_TIMEOUT));
+            return false;
+        }
+        if (*(volatile uint32_t *)status != 0u) return false;  // someone else already failed
+    }
+}
+
+// ---------------------------------------------------------------- activation quantiser
+// The reference's dynamic FP8 activation quantisation, bit for bit
+// (crates/weightstream-ref/src/actquant.rs:21-45; device twin
+// crates/weightstream-cuda/kernels/actquant.cu:47-83): per 32 contiguous values,
+// amax floored at 1e-4, scale 2^ceil(log2(amax/448)) taken from the exponent and
+// mantissa bits of the quotient, value/scale rounded to nearest even onto the
+// E4M3 grid with saturation at +-448.
+__device__ __forceinline__ int act_scale_exp(float amax) {
+    amax = fmaxf(amax, 1e-4f);
+    const uint32_t bits = __float_as_uint(__fdiv_rn(amax, 448.0f));
+    return (int)((bits >> 23) & 0xFF) - 127 + ((bits & 0x7FFFFF) ? 1 : 0);
+}
+__device__ __forceinline__ float pow2_f32(int e) {  // exact for -126 <= e <= 127
+    return __uint_as_float((uint32_t)(e + 127) << 23);
+}
+// Two floats -> two E4M3 bytes (lo = a, hi = b), RNE, saturating, NaN -> 0x7F.
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float a, float b) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(b), "f"(a));
+    return r;
+}
+// Eight values held by one lane (a quarter of a 32-block spread over 4 adjacent
+// lanes): returns the block exponent and the eight E4M3 bytes in k order.
+__device__ __forceinline__ void act_quant8(const float (&v)[8], int &e, uint32_t &lo, uint32_t &hi) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    e = act_scale_exp(amax);
+    const float inv = pow2_f32(-e);
+    lo = cvt_e4m3x2(v[0] * inv, v[1] * inv) | (cvt_e4m3x2(v[2] * inv, v[3] * inv) << 16);
+    hi = cvt_e4m3x2(v[4] * inv, v[5] * inv) | (cvt_e4m3x2(v[6] * inv, v[7] * inv) << 16);
+}
+
+// Load eight consecutive activations (bf16 or f32) as floats, zero beyond `valid`.
+__device__ __forceinline__ void load_act8(const void *base, int x_dtype, int64_t elem_off, bool valid,
+                                          float (&v)[8]) {
+    if (!valid) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+        return;
+    }
+    if (x_dtype == WS_ACT_BF16) {
+        const uint4 r = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(base) + elem_off));
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    } else {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(base) + elem_off));
+        const float4 b = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(base) + elem_off) + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+}
+
+}  // namespace ws
