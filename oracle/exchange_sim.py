@@ -1,0 +1,106 @@
+"""CPU-rank simulation of the one-shot exchange (test infrastructure, like the oracle).
+
+R threads play R ranks.  Each rank owns slot memory double-banked by step parity and one
+flag per (bank, source rank) carrying the step sequence number -- the protocol the CUDA
+kernels run over NVLink, restated on host buffers so that rank order, cross-rank bit
+identity, run-ahead safety and the fail-stop rules can be tested with no GPU:
+
+* every rank stores its vector into slot [bank][my rank] of EVERY rank, then sets the flag
+  (crates/weightstream-transport/src/ring.rs:338-390 does the same in two RDMA hops);
+* a rank waits, with a deadline, until all R flags of the bank carry this step's sequence
+  number (ring.rs:439-458: a timeout aborts the step, nothing is computed on partial data;
+  ring.rs:488-499: a sequence number that is neither this step's nor an earlier one aborts);
+* all-reduce adds the slots left to right in rank order (ring.rs:399-408); all-gather
+  concatenates them (ring.rs:426-432).
+"""
+from __future__ import annotations
+
+import threading
+import time
+from typing import Callable, List, Optional
+
+import numpy as np
+
+
+class ExchangeTimeout(RuntimeError):
+    pass
+
+
+class ExchangeOutOfSequence(RuntimeError):
+    pass
+
+
+class RankMemory:
+    def __init__(self, world: int, elems: int):
+        self.slots = np.zeros((2, world, elems), dtype=np.float32)
+        self.flags = np.zeros((2, world), dtype=np.uint32)
+
+
+class SimGroup:
+    def __init__(self, world: int, elems: int, wait_s: float = 1.0):
+        self.world, self.elems, self.wait_s = world, elems, wait_s
+        self.mem = [RankMemory(world, elems) for _ in range(world)]
+        self.step = [0] * world
+        # fault injection (host side only): drop[(src, dst)] = True loses src's message to dst
+        self.drop = {}
+        self.seq_override = {}
+
+    def _exchange(self, rank: int, vec: np.ndarray) -> int:
+        n = vec.size
+        if n == 0 or n > self.elems:
+            raise ValueError(f"collective input len {n} not in 1..={self.elems}")
+        self.step[rank] += 1
+        seq = self.step[rank]
+        bank = seq & 1
+        send_seq = self.seq_override.get(rank, seq)
+        for p in range(self.world):
+            if self.drop.get((rank, p)):
+                continue
+            self.mem[p].slots[bank, rank, :n] = vec          # data first ...
+            self.mem[p].flags[bank, rank] = send_seq          # ... then the flag (release)
+        deadline = time.monotonic() + self.wait_s
+        mine = self.mem[rank]
+        while True:
+            f = mine.flags[bank].copy()
+            if np.all(f == seq):
+                return bank
+            bad = [int(v) for v in f if v > seq]
+            if bad:
+                raise ExchangeOutOfSequence(f"collective out of sequence: got step {bad[0]} at step {seq} (fail-stop)")
+            if time.monotonic() >= deadline:
+                have = [r for r in range(self.world) if f[r] == seq]
+                raise ExchangeTimeout(f"all-reduce wait timeout after {int(self.wait_s * 1e3)} ms "
+                                      f"(have {have} of {self.world}); fail-stop, aborting")
+            time.sleep(0)
+
+    def allreduce(self, rank: int, vec: np.ndarray) -> np.ndarray:
+        v = np.ascontiguousarray(vec, dtype=np.float32)
+        bank = self._exchange(rank, v)
+        s = self.mem[rank].slots[bank]
+        acc = s[0, :v.size].copy()
+        for r in range(1, self.world):
+            acc = (acc + s[r, :v.size]).astype(np.float32)
+        return acc
+
+    def allgather(self, rank: int, vec: np.ndarray) -> np.ndarray:
+        v = np.ascontiguousarray(vec, dtype=np.float32)
+        bank = self._exchange(rank, v)
+        return self.mem[rank].slots[bank][:, :v.size].reshape(-1).copy()
+
+
+def run_ranks(world: int, fn: Callable[[int], object], skip: Optional[List[int]] = None):
+    """Run fn(rank) on one thread per rank; returns results (or the exception raised)."""
+    out: List[object] = [None] * world
+
+    def body(r):
+        try:
+            out[r] = fn(r)
+        except Exception as e:  # noqa: BLE001 - handed back to the test
+            out[r] = e
+
+    ts = [threading.Thread(target=body, args=(r,)) for r in range(world) if not (skip and r in skip)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    return out

@@ -76,10 +76,14 @@ def test_act_quant_f32_edge_cases(dev, tpmod, oracle):
     x[3, :2] = [3.0e38, -3.0e38]
     q, s = tpmod.act_quant_fp8(torch.from_numpy(x).to(dev))
     torch.cuda.synchronize()
+    def canon(b):  # both NaN codes (S.1111.111) are the same value; which sign a NaN gets is the FPU's choice
+        b = b.copy()
+        b[(b & 0x7F) == 0x7F] = 0x7F
+        return b
     for r in range(4):
         qo, so = oracle.fp8_act_emit(x[r])
-        assert np.array_equal(q[r].cpu().numpy(), qo)
-        assert np.array_equal(s[r].cpu().numpy(), so)
+        assert np.array_equal(canon(q[r].cpu().numpy()), canon(qo)), f"row {r}"
+        assert np.array_equal(s[r].cpu().numpy(), so), f"row {r}"
 
 
 # ----------------------------------------------------------------------------- FP8 GEMM, TP=1
@@ -312,9 +316,10 @@ def test_lm_head_argmax_ties_lowest_index(dev, tpmod, oracle):
     xq = oracle.fp8_snap(F.bf16_bits_to_f32(xb)[0])
     # a row perfectly aligned with x maximises the logit; plant it twice inside one scale block
     best = F.f32_to_e4m3(np.sign(xq) * 448.0)
-    lo, hi = 500, 500 + 64
+    lo, hi = 500, vocab // 2 + 4000    # one on each rank, as gpu.rs:1372 spreads them (500 and 90000)
     w[lo] = best
     w[hi] = best
+    sc[hi // 128] = sc[lo // 128]      # same block scales, so the two logits are the same number
     world = 2
     grp = tpmod.LocalGroup(world, max_m=1, max_n=16, max_vocab=vocab)
     try:

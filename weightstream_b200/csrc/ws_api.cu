@@ -524,7 +524,7 @@ ws_status_t ws_moe_down_combine_allreduce_group(ws_tp_t *const *ranks, int32_t n
     const MoeSmem fixed = moe_smem_layout(0, p.stage_boxes, p.k, p.m, p.top_k, e_len_max, owned_rows);
     int ns = (kSmemBudget - fixed.total) / fixed.stage_bytes;
     if (ns > kMaxStages) ns = kMaxStages;
-    if (ns < 2 || ns * fixed.stage_bytes < p.m * p.top_k * kGroupRows * 4)
+    if (ns < 2)
         return fail(t0, WS_ERR_CAPACITY, "shapes m=%d n=%d k=%d leave no room for the weight stage ring", p.m, p.n, p.k);
     p.nstages = ns;
     const size_t smem = (size_t)moe_smem_layout(ns, p.stage_boxes, p.k, p.m, p.top_k, e_len_max, owned_rows).total + 1024;

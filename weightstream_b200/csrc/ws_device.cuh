@@ -205,8 +205,10 @@ __device__ __forceinline__ int act_scale_exp(float amax) {
     const uint32_t bits = __float_as_uint(__fdiv_rn(amax, 448.0f));
     return (int)((bits >> 23) & 0xFF) - 127 + ((bits & 0x7FFFFF) ? 1 : 0);
 }
-__device__ __forceinline__ float pow2_f32(int e) {  // exact for -126 <= e <= 127
-    return __uint_as_float((uint32_t)(e + 127) << 23);
+__device__ __forceinline__ float pow2_f32(int e) {  // 2^e for any e: inf above 127, subnormal/0 below -126
+    if (e > 127) return __uint_as_float(0x7F800000u);
+    if (e >= -126) return __uint_as_float((uint32_t)(e + 127) << 23);
+    return e >= -149 ? __uint_as_float(1u << (e + 149)) : 0.0f;
 }
 // Two floats -> two E4M3 bytes (lo = a, hi = b), RNE, saturating, NaN -> 0x7F.
 __device__ __forceinline__ uint32_t cvt_e4m3x2(float a, float b) {
@@ -223,7 +225,7 @@ __device__ __forceinline__ void act_quant8(const float (&v)[8], int &e, uint32_t
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     e = act_scale_exp(amax);
-    const float inv = pow2_f32(-e);
+    const float inv = e > 127 ? 0.0f : pow2_f32(-e);  // an infinite block scale divides everything to zero
     lo = cvt_e4m3x2(v[0] * inv, v[1] * inv) | (cvt_e4m3x2(v[2] * inv, v[3] * inv) << 16);
     hi = cvt_e4m3x2(v[4] * inv, v[5] * inv) | (cvt_e4m3x2(v[6] * inv, v[7] * inv) << 16);
 }

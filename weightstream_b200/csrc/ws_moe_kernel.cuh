@@ -47,7 +47,7 @@ struct MoeParams {
 };
 
 struct MoeSmem {
-    int32_t stages, q, sa, red, part, ids, wts, cnt, pstart, pass_e, pass_n, pass_r, bars, misc, total;
+    int32_t stages, q, sa, red, part, yroute, ids, wts, cnt, pstart, pass_e, pass_n, pass_r, bars, misc, total;
     int32_t stage_bytes, scale_off;
 };
 
@@ -63,6 +63,7 @@ __host__ __device__ inline MoeSmem moe_smem_layout(int nstages, int stage_boxes,
     s.sa = o;     o += kb32 * 8 * 4;
     s.red = o;    o += 2 * kConsumerWarps * 128 * 4;
     s.part = o;   o += (int)align_up((int64_t)m * owned_rows * 4, 16);
+    s.yroute = o; o += (int)align_up((int64_t)m * top_k * kGroupRows * 4, 16);  // per-route sums of a leftover group
     s.ids = o;    o += (int)align_up((int64_t)m * top_k * 4, 16);
     s.wts = o;    o += (int)align_up((int64_t)m * top_k * 4, 16);
     s.cnt = o;    o += (int)align_up((int64_t)e_len * 4, 16);
@@ -377,13 +378,12 @@ __global__ void __launch_bounds__(kThreads, 1) moe_down_kernel(const __grid_cons
     const bool empty_rank = p.split && NP == 0 && cta < Rg;
     if (empty_rank) fin[nfin++] = cta;
 
-    // Fold the leftover groups this CTA arrived last at.  Every item this CTA was given has
-    // been consumed, so the stage ring is idle and holds the per-route sums.
+    // Fold the leftover groups this CTA arrived last at.
     for (int f = 0; f < nfin; ++f) {
         const int j = fin[f];
         __threadfence();
         // Phase 1: per route, add the K-split contributions in K order.
-        float *yroute = reinterpret_cast<float *>(smem + S.stages);  // [NR][16]
+        float *yroute = reinterpret_cast<float *>(smem + S.yroute);  // [NR][16]
         for (int ps = 0; ps < NP; ++ps) {
             const int64_t pair = (int64_t)j * NP + ps;
             const int ca = owner_of(pair * kbox, U, ncta), cb = owner_of((pair + 1) * kbox - 1, U, ncta);

@@ -65,8 +65,9 @@ def shard_weight(view, shape: Sequence[int], shard: WShard, align: int = 32):
     rows, cols = shape
     if shard.kind == "all":
         return view
-    if view.numel() if hasattr(view, "numel") else view.size != rows * cols:
-        raise ValueError(f"weight bytes do not tile [{rows}, {cols}]")
+    count = view.numel() if hasattr(view, "numel") else view.size
+    if count != rows * cols:
+        raise ValueError(f"weight bytes {count} do not tile [{rows}, {cols}]")
     m = view.reshape(rows, cols)
     if shard.kind == "rows":
         if shard.start % align or shard.len % align or shard.start + shard.len > rows:
@@ -132,7 +133,7 @@ def _fp8_args(x, w, scales, block, row0, k0, out) -> Fp8GemmArgs:
     if w.shape[1] != k:
         raise ValueError(f"x has k={k} but w has {w.shape[1]} columns")
     a = Fp8GemmArgs()
-    a.x, a.ldx, a.x_dtype = x.data_ptr(), x.stride(0), _act_dtype(x)
+    a.x, a.ldx, a.x_dtype = x.data_ptr(), (x.stride(0) if m > 1 else k), _act_dtype(x)
     a.m, a.n, a.k = m, n, k
     a.w, a.ldw = w.data_ptr(), w.stride(0)
     a.scales, a.scale_ld, a.scale_kind = scales.data_ptr(), scales.shape[1], _scale_kind(scales)
@@ -300,7 +301,7 @@ def _moe_args(h, route_ids, route_w, w2, s2, e_start, out) -> MoeDownArgs:
     e_len, n, half = w2.shape
     m, top_k = route_ids.shape
     a = MoeDownArgs()
-    a.h, a.ldh, a.h_dtype = h.data_ptr(), h.stride(0), _act_dtype(h)
+    a.h, a.ldh, a.h_dtype = h.data_ptr(), (h.stride(0) if h.shape[0] > 1 else half * 2), _act_dtype(h)
     a.m, a.n, a.k, a.top_k = m, n, half * 2, top_k
     a.route_ids, a.route_w = route_ids.data_ptr(), route_w.data_ptr()
     a.w2, a.s2 = w2.data_ptr(), s2.data_ptr()
