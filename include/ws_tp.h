@@ -106,7 +106,7 @@ typedef struct {
     const void *scales;       /* scale matrix this rank holds                                         */
     int64_t scale_ld;         /* elements per scale row                                               */
     int32_t scale_kind;       /* WS_SCALE_UE8M0 (reference: 32x32) or WS_SCALE_F32 (128x128)          */
-    int32_t block_n, block_k; /* scale block shape; block_n multiple of 16, block_k multiple of 32    */
+    int32_t block_n, block_k; /* scale block shape; powers of two, block_n >= 16, block_k >= 32       */
     int64_t row0, k0;         /* offset of w[0,0] inside the held scale matrix (row0 multiple of 16)  */
     float *out;               /* [m, n] fp32, row stride n                                            */
 } ws_fp8_gemm_args_t;

@@ -329,8 +329,8 @@ static ws_status_t validate_fp8(ws_tp *tp, const ws_fp8_gemm_args_t &a, bool lm_
     if ((reinterpret_cast<uintptr_t>(a.x) & 15) || (a.ldx % xa) || a.ldx < a.k)
         return fail(tp, WS_ERR_INVALID, "x must be 16-byte aligned with ldx >= k and ldx a multiple of %d", xa);
     if (a.scale_kind != WS_SCALE_UE8M0 && a.scale_kind != WS_SCALE_F32) return fail(tp, WS_ERR_INVALID, "bad scale_kind");
-    if (a.block_n < 16 || a.block_n % 16 || a.block_k < 32 || a.block_k % 32)
-        return fail(tp, WS_ERR_INVALID, "scale block %dx%d: block_n must be a multiple of 16, block_k of 32", a.block_n, a.block_k);
+    if (a.block_n < 16 || (a.block_n & (a.block_n - 1)) || a.block_k < 32 || (a.block_k & (a.block_k - 1)))
+        return fail(tp, WS_ERR_INVALID, "scale block %dx%d: block_n must be a power of two >= 16, block_k >= 32", a.block_n, a.block_k);
     if (a.row0 < 0 || a.k0 < 0 || a.row0 % 16) return fail(tp, WS_ERR_INVALID, "row0 must be a non-negative multiple of 16");
     if ((a.k0 + a.k - 1) / a.block_k >= a.scale_ld) return fail(tp, WS_ERR_INVALID, "k slice reaches past scale_ld");
     if (a.ldw < a.k) return fail(tp, WS_ERR_INVALID, "ldw < k");
@@ -347,6 +347,8 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
     Fp8Params p{};
     p.m = mt; p.n = a0.n; p.k = a0.k; p.x_dtype = a0.x_dtype; p.scale_kind = a0.scale_kind;
     p.bn = a0.block_n; p.bk = a0.block_k; p.world = t0->world;
+    for (p.bk_shift = 0; (1 << p.bk_shift) < p.bk; ++p.bk_shift) {}
+    for (p.bn_shift = 0; (1 << p.bn_shift) < p.bn; ++p.bn_shift) {}
     p.mode = lm ? kModeLmHead : kModeAllReduce;
     p.vocab = lm ? lm[0].vocab : 0;
     p.gather_logits = 0;

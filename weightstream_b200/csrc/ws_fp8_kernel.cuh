@@ -44,6 +44,7 @@ struct Fp8Params {
     int32_t m, n, k, x_dtype, scale_kind, bn, bk;
     int32_t world, mode, vocab, mp, nstages, nslot_max, skb;
     int32_t gather_logits, split;
+    int32_t bk_shift, bn_shift;  // log2 of the scale block edges
     uint32_t seq, pad1;
     uint64_t timeout_ns;
     SymLayout lay;
@@ -191,16 +192,16 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_rowpar_kernel(const __grid_co
         }
     }
     // Prologue 2: weight scales of the rows this CTA touches, as fp32.
-    const int64_t kcol0 = A.k0 / p.bk;
-    const int64_t srow_lo = (A.row0 + (int64_t)g0 * kGroupRows) / p.bn;
-    const int nslotA = Gm ? (int)((A.row0 + (int64_t)(g0 + Gm) * kGroupRows - 1) / p.bn - srow_lo + 1) : 0;
+    const int64_t kcol0 = A.k0 >> p.bk_shift;
+    const int64_t srow_lo = (A.row0 + (int64_t)g0 * kGroupRows) >> p.bn_shift;
+    const int nslotA = Gm ? (int)(((A.row0 + (int64_t)(g0 + Gm) * kGroupRows - 1) >> p.bn_shift) - srow_lo + 1) : 0;
     {
-        const int ncols = (int)((A.k0 + p.k - 1) / p.bk - kcol0 + 1);
+        const int ncols = (int)(((A.k0 + p.k - 1) >> p.bk_shift) - kcol0 + 1);
         const int nslots = nslotA + extra + nruns;
         for (int i = tid; i < nslots * ncols; i += kConsumerThreads) {
             const int sl = i / ncols, c = i - sl * ncols;
             const int lg = (extra && sl == nslotA) ? Gm * ncta + cta : Gm * ncta + jfirst + (sl - nslotA - extra);
-            const int64_t srow = sl < nslotA ? srow_lo + sl : (A.row0 + (int64_t)lg * kGroupRows) / p.bn;
+            const int64_t srow = sl < nslotA ? srow_lo + sl : (A.row0 + (int64_t)lg * kGroupRows) >> p.bn_shift;
             const int64_t idx = srow * A.scale_ld + kcol0 + c;
             float s;
             if (p.scale_kind == WS_SCALE_UE8M0) {
@@ -222,34 +223,46 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_rowpar_kernel(const __grid_co
     int item = 0;
     int redbuf = 0;
 
+    const int kofs = (int)(A.k0 - kcol0 * p.bk);  // k0 modulo the scale block
+    auto mma_step = [&](uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, int kb, const float *swrow) {
+        uint32_t b0r = 0, b1r = 0;
+        if (g < p.mp) {
+            const uint8_t *qp = q_s + ((size_t)(kb * p.mp + g) * 32 + tq * 4);
+            b0r = *reinterpret_cast<const uint32_t *>(qp);
+            b1r = *reinterpret_cast<const uint32_t *>(qp + 16);
+        }
+        float d[4];
+        mma_e4m3_16x8x32(d, a0, a1, a2, a3, b0r, b1r);
+        const float2 sa = *reinterpret_cast<const float2 *>(sa_s + kb * 8 + tq * 2);
+        const float sw = swrow[(kofs + kb * 32) >> p.bk_shift];
+        const float f0 = sa.x * sw, f1 = sa.y * sw;
+        acc[0] = fmaf(d[0], f0, acc[0]);
+        acc[1] = fmaf(d[1], f1, acc[1]);
+        acc[2] = fmaf(d[2], f0, acc[2]);
+        acc[3] = fmaf(d[3], f1, acc[3]);
+    };
     auto run_item = [&](int b0, int nb, int slot) {
         const int s = item % NS;
         mbar_wait(full0 + s * 8, (uint32_t)(item / NS) & 1u, X.status);
         const uint32_t sbase = stage0 + s * kStageBytes;
+        const float *swrow = sw_s + slot * p.skb;
+        const uint32_t sw7 = (uint32_t)(lm_row & 7);
         for (int bi = warp; bi < nb; bi += kConsumerWarps) {
             const int box = b0 + bi;
             const uint32_t bbase = sbase + bi * kBoxBytes + lm_row * 128;
+            if (box * 4 + 4 <= kb32) {  // full box: issue the four fragment loads together
+                uint32_t a[4][4];
 #pragma unroll
-            for (int kq = 0; kq < 4; ++kq) {
-                const int kb = box * 4 + kq;
-                if (kb >= kb32) break;
-                uint32_t a0, a1, a2, a3;
-                ldmatrix_x4(bbase + ((((kq << 1) | lm_hi) ^ (lm_row & 7)) << 4), a0, a1, a2, a3);
-                uint32_t b0r = 0, b1r = 0;
-                if (g < p.mp) {
-                    const uint8_t *qp = q_s + ((size_t)(kb * p.mp + g) * 32 + tq * 4);
-                    b0r = *reinterpret_cast<const uint32_t *>(qp);
-                    b1r = *reinterpret_cast<const uint32_t *>(qp + 16);
+                for (int kq = 0; kq < 4; ++kq)
+                    ldmatrix_x4(bbase + ((((uint32_t)(kq << 1) | lm_hi) ^ sw7) << 4), a[kq][0], a[kq][1], a[kq][2], a[kq][3]);
+#pragma unroll
+                for (int kq = 0; kq < 4; ++kq) mma_step(a[kq][0], a[kq][1], a[kq][2], a[kq][3], box * 4 + kq, swrow);
+            } else {
+                for (int kq = 0; kq < 4 && box * 4 + kq < kb32; ++kq) {
+                    uint32_t a0, a1, a2, a3;
+                    ldmatrix_x4(bbase + ((((uint32_t)(kq << 1) | lm_hi) ^ sw7) << 4), a0, a1, a2, a3);
+                    mma_step(a0, a1, a2, a3, box * 4 + kq, swrow);
                 }
-                float d[4];
-                mma_e4m3_16x8x32(d, a0, a1, a2, a3, b0r, b1r);
-                const float2 sa = *reinterpret_cast<const float2 *>(sa_s + kb * 8 + tq * 2);
-                const float sw = sw_s[slot * p.skb + (int)((A.k0 + (int64_t)kb * 32) / p.bk - kcol0)];
-                const float f0 = sa.x * sw, f1 = sa.y * sw;
-                acc[0] = fmaf(d[0], f0, acc[0]);
-                acc[1] = fmaf(d[1], f1, acc[1]);
-                acc[2] = fmaf(d[2], f0, acc[2]);
-                acc[3] = fmaf(d[3], f1, acc[3]);
             }
         }
         __syncwarp();
@@ -283,7 +296,7 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_rowpar_kernel(const __grid_co
     // ---- owned groups
     for (int gi = 0; gi < n_own; ++gi) {
         acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
-        const int slot = gi < Gm ? (int)((A.row0 + (int64_t)(g0 + gi) * kGroupRows) / p.bn - srow_lo) : nslotA;
+        const int slot = gi < Gm ? (int)(((A.row0 + (int64_t)(g0 + gi) * kGroupRows) >> p.bn_shift) - srow_lo) : nslotA;
         for (int b0 = 0; b0 < kbox; b0 += kBoxesPerStage) run_item(b0, min(kBoxesPerStage, kbox - b0), slot);
         const float v = reduce_warps();
         if (tid < 128 && tok_t < p.m) part_s[tok_t * owned_rows + gi * kGroupRows + row_t] = v;
@@ -319,11 +332,21 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_rowpar_kernel(const __grid_co
         __threadfence();
         float sum = 0.0f;
         if (tid < 128) {
-            for (int c = c_lo; c <= c_hi; ++c) {
-                const int64_t cb = unit_begin(c, U, ncta);
-                if (unit_begin(c + 1, U, ncta) == cb) continue;  // this CTA holds no unit
-                const int jf = (int)(cb / kbox);
-                sum += ld_volatile_f32(X.contrib + ((size_t)c * kMaxRuns + (j - jf)) * (8 * kGroupRows) + tid);
+            // contributions in CTA (= K) order; loads are issued eight at a time, adds stay ordered
+            for (int c = c_lo; c <= c_hi; c += 8) {
+                float v[8];
+                bool has[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int cc = c + i;
+                    const int64_t cb = unit_begin(cc, U, ncta);
+                    has[i] = cc <= c_hi && unit_begin(cc + 1, U, ncta) > cb;
+                    const int jf = (int)(cb / kbox);
+                    v[i] = has[i] ? __ldcg(X.contrib + ((size_t)cc * kMaxRuns + (j - jf)) * (8 * kGroupRows) + tid) : 0.0f;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (has[i]) sum += v[i];
             }
         }
         // `sum` is this rank's partial of leftover group j at (row_t, tok_t)
