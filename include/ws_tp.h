@@ -185,6 +185,30 @@ ws_status_t ws_act_quant_fp8(const void *x, int64_t ldx, int32_t x_dtype, int32_
  * the same number of bytes; 0 hands each leftover group to one CTA whole. */
 ws_status_t ws_tp_set_split(ws_tp_t *tp, int32_t on);
 
+/* ---- FP8 GEMM for callers that must not allocate ------------------------------------------
+ * No counterpart in the reference.  Some hosts embed this library where device memory may
+ * not be allocated on their behalf: a runtime that hands out one fixed arena at start-up and
+ * forbids cudaMalloc afterwards, code running inside a memory-pool or capture-style region
+ * where an allocation is an error, or a plug-in that has no endpoint (ws_tp_create allocates
+ * the exchange region).  This is the single-rank form of ws_fp8_rowpar_gemm_allreduce (same
+ * arguments, same kernel, out = the whole sum since there is one rank) whose scratch -- the
+ * K-split partial sums, their arrival counters and a status word -- is a fixed array inside
+ * the library image (WS_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the
+ * process exits).  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ *  - limits: m <= WS_STATIC_MAX_M and n <= WS_STATIC_MAX_N; beyond them WS_ERR_CAPACITY with a
+ *    message in `err` (optional buffer of err_len bytes).
+ *  - the first call on a device looks the array's device address up and raises the kernel's
+ *    shared-memory limit; make that first call before any stream capture begins.
+ *  - all calls on a device share the one array, which keeps the previous call's contents; the
+ *    entry point clears the counters and the status word on `stream` before the kernel.  Two
+ *    calls that overlap on the GPU (different streams, no ordering) race on it. */
+#define WS_STATIC_MAX_M 8
+#define WS_STATIC_MAX_N 1048576
+#define WS_STATIC_SCRATCH_BYTES (160 * 16 * 8 * 16 * 4 + (160 + 8) * 4)
+ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *args, int32_t device, void *stream,
+                                       char *err, size_t err_len);
+
 const char *ws_version(void);
 
 #ifdef __cplusplus

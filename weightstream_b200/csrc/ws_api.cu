@@ -703,4 +703,111 @@ ws_status_t ws_tp_set_split(ws_tp_t *tp, int32_t on) {
     return WS_OK;
 }
 
+
+// ------------------------------------------------------------------------------ no allocation
+// Scratch for ws_fp8_gemm_static_scratch: the K-split contributions of every CTA, the
+// arrival counters of the split row groups and one status word.  It lives in the library
+// image, so every GPU that loads the library holds these bytes until the process exits.
+constexpr size_t kStaticContribFloats = (size_t)kMaxCtas * kMaxRuns * 8 * kGroupRows;
+constexpr size_t kStaticScratchBytes = kStaticContribFloats * sizeof(float) + (kMaxShared + 8) * sizeof(uint32_t);
+static_assert(kStaticScratchBytes == WS_STATIC_SCRATCH_BYTES, "header and library disagree on the scratch size");
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kStaticMaxDevices = 64;
+unsigned char *g_static_scratch_addr[kStaticMaxDevices] = {};
+int g_static_sm_count[kStaticMaxDevices] = {};
+std::mutex g_static_mutex;
+
+void set_err(char *err, size_t len, const char *fmt, ...) {
+    if (!err || !len) return;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(err, len, fmt, ap);
+    va_end(ap);
+}
+}  // namespace
+
+ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *a, int32_t device, void *stream, char *err,
+                                       size_t err_len) {
+    if (err && err_len) err[0] = 0;
+    if (!a) { set_err(err, err_len, "null args"); return WS_ERR_INVALID; }
+    if (device < 0 || device >= kStaticMaxDevices) { set_err(err, err_len, "device %d out of range", device); return WS_ERR_INVALID; }
+    ws_tp probe_err;  // only carries validate_fp8's message; owns no device memory
+    ws_status_t st = validate_fp8(&probe_err, *a, false);
+    if (st != WS_OK) { set_err(err, err_len, "%s", probe_err.err.c_str()); return st; }
+    if (a->m > WS_STATIC_MAX_M) {
+        set_err(err, err_len, "m=%d exceeds the %d activation rows the static scratch is laid out for", a->m, WS_STATIC_MAX_M);
+        return WS_ERR_CAPACITY;
+    }
+    if (a->n > WS_STATIC_MAX_N) {
+        set_err(err, err_len, "n=%d exceeds the static-scratch limit of %d output rows", a->n, WS_STATIC_MAX_N);
+        return WS_ERR_CAPACITY;
+    }
+    cudaError_t ce = cudaSetDevice(device);
+    if (ce != cudaSuccess) { set_err(err, err_len, "cudaSetDevice(%d): %s", device, cudaGetErrorString(ce)); return WS_ERR_CUDA; }
+    {   // set-up, once per device, with that device current: the array's name is only a host-side
+        // stand-in, the address a kernel may use comes from cudaGetSymbolAddress
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!g_static_scratch_addr[device]) {
+            void *ptr = nullptr;
+            ce = cudaGetSymbolAddress(&ptr, g_static_scratch);
+            if (ce != cudaSuccess || !ptr) {
+                set_err(err, err_len, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(ce));
+                return WS_ERR_CUDA;
+            }
+            int sms = 0;
+            ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+            if (ce == cudaSuccess) ce = cudaFuncSetAttribute(fp8_rowpar_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (ce != cudaSuccess) { set_err(err, err_len, "device set-up: %s", cudaGetErrorString(ce)); return WS_ERR_CUDA; }
+            g_static_sm_count[device] = sms;
+            g_static_scratch_addr[device] = static_cast<unsigned char *>(ptr);
+        }
+    }
+    unsigned char *base = g_static_scratch_addr[device];
+    const int ncta = std::min(g_static_sm_count[device], (int)kMaxCtas);
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    // counters and the status word must start at zero; the contributions are always written
+    // before they are read, so what the previous call left there does not matter
+    ce = cudaMemsetAsync(base + kStaticContribFloats * sizeof(float), 0, (kMaxShared + 8) * sizeof(uint32_t), cs);
+    if (ce != cudaSuccess) { set_err(err, err_len, "cudaMemsetAsync: %s", cudaGetErrorString(ce)); return WS_ERR_CUDA; }
+
+    Fp8Params p{};
+    p.m = a->m; p.n = a->n; p.k = a->k; p.x_dtype = a->x_dtype; p.scale_kind = a->scale_kind;
+    p.bn = a->block_n; p.bk = a->block_k; p.world = 1; p.mode = kModeAllReduce;
+    for (p.bk_shift = 0; (1 << p.bk_shift) < p.bk; ++p.bk_shift) {}
+    for (p.bn_shift = 0; (1 << p.bn_shift) < p.bn; ++p.bn_shift) {}
+    p.mp = p.m <= 1 ? 1 : p.m <= 2 ? 2 : p.m <= 4 ? 4 : 8;
+    p.split = 1;
+    p.timeout_ns = 2000000000ull;
+    const int kbox = (p.k + 127) / 128;
+    const int G = p.n / kGroupRows, Gm = G / ncta, Rg = G - Gm * ncta;
+    p.skb = (int)((a->k0 + a->k - 1) / a->block_k - a->k0 / a->block_k + 1);
+    p.nslot_max = (Gm * kGroupRows) / p.bn + 2 + 1 + 4;
+    if (Rg) {
+        const int64_t U = (int64_t)Rg * kbox, per = (U + ncta - 1) / ncta;
+        if ((per + kbox - 1) / kbox + 1 > 4) p.split = 0;
+    }
+    const int owned_rows = (Gm + ((!p.split && Rg) ? 1 : 0)) * kGroupRows;
+    const Fp8Smem fixed = fp8_smem_layout(0, kbox, p.mp, p.nslot_max, p.skb, p.m, owned_rows);
+    int ns = std::min((kSmemBudget - fixed.total) / kStageBytes, (int)kMaxStages);
+    if (ns < 2) { set_err(err, err_len, "shapes m=%d n=%d k=%d leave no room for the weight stage ring", p.m, p.n, p.k); return WS_ERR_CAPACITY; }
+    p.nstages = ns;
+    const size_t smem = (size_t)fp8_smem_layout(ns, kbox, p.mp, p.nslot_max, p.skb, p.m, owned_rows).total + 1024;
+    Fp8RankArgs &r = p.r[0];
+    st = make_tmap(&probe_err, &r.tmap, a->w, (uint64_t)a->n, (uint64_t)a->k, (uint64_t)a->ldw);
+    if (st != WS_OK) { set_err(err, err_len, "%s", probe_err.err.c_str()); return st; }
+    r.x = a->x; r.scales = a->scales; r.out = a->out;
+    r.ldx = a->ldx; r.scale_ld = a->scale_ld; r.row0 = a->row0; r.k0 = a->k0;
+    r.ctx.contrib = reinterpret_cast<float *>(base);
+    r.ctx.counters = reinterpret_cast<uint32_t *>(base + kStaticContribFloats * sizeof(float));
+    r.ctx.status = r.ctx.counters + kMaxShared;
+    r.ctx.rank = 0;
+    p.seq = 1;
+    fp8_rowpar_kernel<<<dim3((unsigned)ncta, 1, 1), kThreads, smem, cs>>>(p);
+    ce = cudaGetLastError();
+    if (ce != cudaSuccess) { set_err(err, err_len, "kernel launch: %s", cudaGetErrorString(ce)); return WS_ERR_CUDA; }
+    return WS_OK;
+}
+
 }  // extern "C"
