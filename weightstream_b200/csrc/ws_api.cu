@@ -82,16 +82,16 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// Row-major byte matrix [rows][row_bytes] with stride `ld` bytes, 128 x 16 boxes, 128B swizzle.
+// Row-major byte matrix [rows][row_bytes] with stride `ld` bytes, boxes of 128 bytes x box_rows, 128B swizzle.
 ws_status_t make_tmap(ws_tp *tp, CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes,
-                      uint64_t ld) {
+                      uint64_t ld, uint32_t box_rows = kGroupRows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(tp, WS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld & 15))
         return fail(tp, WS_ERR_INVALID, "weight base and row stride must be multiples of 16 bytes");
     cuuint64_t dims[2] = {row_bytes, rows};
     cuuint64_t strides[1] = {ld};
-    cuuint32_t box[2] = {128, (cuuint32_t)kGroupRows};
+    cuuint32_t box[2] = {128, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -100,12 +100,22 @@ ws_status_t make_tmap(ws_tp *tp, CUtensorMap *map, const void *base, uint64_t ro
     return WS_OK;
 }
 
+// Row granularity of the ragged share of leftover rows: small when each CTA gets a row or two
+// (balance matters, few boxes), larger when it gets many (fewer, bigger TMA boxes).
+int ragged_granularity(int n, int ncta) {
+    const int Gm = n / kGroupRows / ncta;
+    const int L = n - Gm * ncta * kGroupRows;
+    const int per = L / ncta;  // whole rows per CTA
+    return per >= 8 ? 4 : per >= 4 ? 2 : 1;
+}
+
 RankCtx make_ctx(const ws_tp *tp) {
     RankCtx c{};
     for (int i = 0; i < WS_MAX_WORLD; ++i) c.sym[i] = tp->peers[i];
     c.contrib = tp->contrib;
     c.counters = tp->counters;
     c.status = tp->status;
+    c.step_ctr = tp->counters + kMaxShared + 2;
     c.rank = tp->rank;
     return c;
 }
@@ -353,11 +363,10 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
     p.vocab = lm ? lm[0].vocab : 0;
     p.gather_logits = 0;
     p.mp = mt <= 1 ? 1 : mt <= 2 ? 2 : mt <= 4 ? 4 : 8;
-    p.split = t0->split;
     p.timeout_ns = t0->timeout_ns;
     p.lay = t0->lay;
     const int kbox = (p.k + 127) / 128;
-    const int G = p.n / kGroupRows, Gm = G / ncta, Rg = G - Gm * ncta;
+    const int Gm = p.n / kGroupRows / ncta;
     int64_t skb = 1;
     for (int i = 0; i < n; ++i) {
         const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
@@ -365,26 +374,28 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
         if (lm && lm[i].logits) p.gather_logits = 1;
     }
     p.skb = (int)skb;
-    p.nslot_max = (Gm * kGroupRows) / p.bn + 2 + 1 + 4;
-    const int owned_rows = (Gm + ((!p.split && Rg) ? 1 : 0)) * kGroupRows;
-    if (p.split && Rg) {
-        const int64_t U = (int64_t)Rg * kbox;
-        const int64_t per = (U + ncta - 1) / ncta;
-        if ((per + kbox - 1) / kbox + 1 > 4) p.split = 0;  // would need more scale slots than planned
-    }
-    const Fp8Smem fixed = fp8_smem_layout(0, kbox, p.mp, p.nslot_max, p.skb, p.m, owned_rows);
+    // Ragged leftover rows pay off when a CTA holds only a few tiles (7168 rows: 3 tiles + 1 row instead
+    // of 4 tiles on four CTAs); with many tiles per CTA one whole extra tile is within 2 % of balance.
+    p.ragged = (t0->split && Gm < 8) ? 1 : 0;
+    p.gran = ragged_granularity(p.n, ncta);
+    p.nslot_max = (Gm * kGroupRows) / p.bn + 2 + 2;
+    p.part_rows = (Gm + 2) * kGroupRows;  // whole tiles + at most two ragged tiles
+    const Fp8Smem fixed = fp8_smem_layout(0, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows);
     int ns = (kSmemBudget - fixed.total) / kStageBytes;
     if (ns > kMaxStages) ns = kMaxStages;
     if (ns < 2) return fail(t0, WS_ERR_CAPACITY, "shapes m=%d n=%d k=%d leave no room for the weight stage ring", p.m, p.n, p.k);
     p.nstages = ns;
-    const size_t smem = (size_t)fp8_smem_layout(ns, kbox, p.mp, p.nslot_max, p.skb, p.m, owned_rows).total + 1024;
+    const size_t smem = (size_t)fp8_smem_layout(ns, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows).total + 1024;
 
     for (int i = 0; i < n; ++i) {
         ws_tp *t = ranks[i];
         const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
         Fp8RankArgs &r = p.r[i];
-        ws_status_t s = make_tmap(t, &r.tmap, a.w, (uint64_t)a.n, (uint64_t)a.k, (uint64_t)a.ldw);
-        if (s != WS_OK) { t0->err = t->err; return s; }
+        for (int b = 0; b < 2; ++b) {
+            ws_status_t s = make_tmap(t, &p.tmap[i][b], a.w, (uint64_t)a.n, (uint64_t)a.k, (uint64_t)a.ldw,
+                                      b ? (uint32_t)p.gran : (uint32_t)kGroupRows);
+            if (s != WS_OK) { t0->err = t->err; return s; }
+        }
         const size_t xes = a.x_dtype == WS_ACT_BF16 ? 2 : 4;
         r.x = static_cast<const char *>(a.x) + (size_t)m0 * a.ldx * xes;
         r.scales = a.scales;
@@ -397,7 +408,6 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
     }
     // every endpoint advances by one step
     for (int i = 0; i < n; ++i) ranks[i]->step++;
-    p.seq = (uint32_t)t0->step;
     if (same_device) {
         WS_CUDA(t0, cudaSetDevice(t0->device));
         return launch(t0, fp8_rowpar_kernel, p, ncta, n, kThreads, smem, static_cast<cudaStream_t>(streams ? streams[0] : nullptr));
@@ -405,6 +415,8 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
     for (int i = 0; i < n; ++i) {  // one launch per device, each sees itself as virtual rank 0
         Fp8Params q = p;
         q.r[0] = p.r[i];
+        q.tmap[0][0] = p.tmap[i][0];
+        q.tmap[0][1] = p.tmap[i][1];
         WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
         ws_status_t s = launch(ranks[i], fp8_rowpar_kernel, q, ncta, 1, kThreads, smem,
                                static_cast<cudaStream_t>(streams ? streams[i] : nullptr));
@@ -541,7 +553,6 @@ ws_status_t ws_moe_down_combine_allreduce_group(ws_tp_t *const *ranks, int32_t n
         if (a.e_len != e_len_max) return fail(t0, WS_ERR_INVALID, "ranks must hold equally many experts");
     }
     for (int i = 0; i < n; ++i) ranks[i]->step++;
-    p.seq = (uint32_t)t0->step;
     if (same) {
         WS_CUDA(t0, cudaSetDevice(t0->device));
         return launch(t0, moe_down_kernel, p, ncta, n, kThreads, smem, static_cast<cudaStream_t>(streams ? streams[0] : nullptr));
@@ -584,7 +595,6 @@ static ws_status_t coll_group(ws_tp_t *const *ranks, int n, const float *const *
     }
     ncta = (int)std::min<int64_t>(ncta, std::max<int64_t>(1, len / 256));
     for (int i = 0; i < n; ++i) ranks[i]->step++;
-    p.seq = (uint32_t)t0->step;
     if (same) {
         WS_CUDA(t0, cudaSetDevice(t0->device));
         return launch(t0, coll_kernel, p, ncta, n, 256, 0, static_cast<cudaStream_t>(streams ? streams[0] : nullptr));
@@ -699,7 +709,7 @@ ws_status_t ws_act_quant_fp8(const void *x, int64_t ldx, int32_t x_dtype, int32_
 // Testing knob: 0 makes the leftover row groups whole-CTA work instead of K-split work.
 ws_status_t ws_tp_set_split(ws_tp_t *tp, int32_t on) {
     if (!tp) return WS_ERR_INVALID;
-    tp->split = on ? 1 : 0;
+    tp->split = on < 0 ? 0 : (on > 2 ? 2 : on);
     return WS_OK;
 }
 
@@ -778,36 +788,40 @@ ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *a, int32_t devi
     for (p.bk_shift = 0; (1 << p.bk_shift) < p.bk; ++p.bk_shift) {}
     for (p.bn_shift = 0; (1 << p.bn_shift) < p.bn; ++p.bn_shift) {}
     p.mp = p.m <= 1 ? 1 : p.m <= 2 ? 2 : p.m <= 4 ? 4 : 8;
-    p.split = 1;
     p.timeout_ns = 2000000000ull;
     const int kbox = (p.k + 127) / 128;
-    const int G = p.n / kGroupRows, Gm = G / ncta, Rg = G - Gm * ncta;
+    const int Gm = p.n / kGroupRows / ncta;
     p.skb = (int)((a->k0 + a->k - 1) / a->block_k - a->k0 / a->block_k + 1);
-    p.nslot_max = (Gm * kGroupRows) / p.bn + 2 + 1 + 4;
-    if (Rg) {
-        const int64_t U = (int64_t)Rg * kbox, per = (U + ncta - 1) / ncta;
-        if ((per + kbox - 1) / kbox + 1 > 4) p.split = 0;
-    }
-    const int owned_rows = (Gm + ((!p.split && Rg) ? 1 : 0)) * kGroupRows;
-    const Fp8Smem fixed = fp8_smem_layout(0, kbox, p.mp, p.nslot_max, p.skb, p.m, owned_rows);
+    p.nslot_max = (Gm * kGroupRows) / p.bn + 2 + 2;
+    p.ragged = Gm < 8 ? 1 : 0;
+    p.gran = ragged_granularity(p.n, ncta);
+    p.part_rows = (Gm + 2) * kGroupRows;
+    const Fp8Smem fixed = fp8_smem_layout(0, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows);
     int ns = std::min((kSmemBudget - fixed.total) / kStageBytes, (int)kMaxStages);
     if (ns < 2) { set_err(err, err_len, "shapes m=%d n=%d k=%d leave no room for the weight stage ring", p.m, p.n, p.k); return WS_ERR_CAPACITY; }
     p.nstages = ns;
-    const size_t smem = (size_t)fp8_smem_layout(ns, kbox, p.mp, p.nslot_max, p.skb, p.m, owned_rows).total + 1024;
+    const size_t smem = (size_t)fp8_smem_layout(ns, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows).total + 1024;
     Fp8RankArgs &r = p.r[0];
-    st = make_tmap(&probe_err, &r.tmap, a->w, (uint64_t)a->n, (uint64_t)a->k, (uint64_t)a->ldw);
-    if (st != WS_OK) { set_err(err, err_len, "%s", probe_err.err.c_str()); return st; }
+    for (int b = 0; b < 2; ++b) {
+        st = make_tmap(&probe_err, &p.tmap[0][b], a->w, (uint64_t)a->n, (uint64_t)a->k, (uint64_t)a->ldw,
+                       b ? (uint32_t)p.gran : (uint32_t)kGroupRows);
+        if (st != WS_OK) { set_err(err, err_len, "%s", probe_err.err.c_str()); return st; }
+    }
     r.x = a->x; r.scales = a->scales; r.out = a->out;
     r.ldx = a->ldx; r.scale_ld = a->scale_ld; r.row0 = a->row0; r.k0 = a->k0;
     r.ctx.contrib = reinterpret_cast<float *>(base);
     r.ctx.counters = reinterpret_cast<uint32_t *>(base + kStaticContribFloats * sizeof(float));
     r.ctx.status = r.ctx.counters + kMaxShared;
+    r.ctx.step_ctr = r.ctx.counters + kMaxShared + 2;
     r.ctx.rank = 0;
-    p.seq = 1;
     fp8_rowpar_kernel<<<dim3((unsigned)ncta, 1, 1), kThreads, smem, cs>>>(p);
     ce = cudaGetLastError();
     if (ce != cudaSuccess) { set_err(err, err_len, "kernel launch: %s", cudaGetErrorString(ce)); return WS_ERR_CUDA; }
     return WS_OK;
 }
+
+#ifdef WS_TRACE
+void ws_debug_read_trace(unsigned long long *out) { cudaMemcpyFromSymbol(out, g_ws_trace, sizeof(g_ws_trace)); }
+#endif
 
 }  // extern "C"

@@ -65,6 +65,7 @@ struct RankCtx {
     float *contrib;           // local: [kMaxCtas][kMaxRuns][8*16] split contributions
     uint32_t *counters;       // local: [kMaxShared] arrival counters (self-resetting)
     uint32_t *status;         // local: first error wins
+    uint32_t *step_ctr;       // local: [0] steps completed by this rank, [1] CTAs done with the current step
     int32_t rank;
     int32_t pad;
 };
@@ -150,7 +151,7 @@ __device__ __forceinline__ void mma_e4m3_16x8x32(float (&d)[4], uint32_t a0, uin
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
-__device__ __forceinline__ void consumer_bar() {  // the 8 consumer warps only
+__device__ __forceinline__ void consumer_bar() {  // the consumer warps only
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
 }
 
@@ -190,6 +191,26 @@ __device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t seq, ui
             return false;
         }
         if (*(volatile uint32_t *)status != 0u) return false;  // someone else already failed
+    }
+}
+
+// ---------------------------------------------------------------- step sequence
+// The step number that tags flags and selects the slot bank lives in device memory, so a
+// captured CUDA graph can be replayed: every CTA reads it when the kernel starts, and the last
+// CTA to finish publishes the next value for the kernel that follows on the stream.
+__device__ __forceinline__ uint32_t step_begin(const RankCtx &X) {
+    return *reinterpret_cast<volatile uint32_t *>(X.step_ctr) + 1u;
+}
+__device__ __forceinline__ void step_end(const RankCtx &X, uint32_t seq, uint32_t ncta) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const uint32_t prev = atomicAdd(X.step_ctr + 1, 1u);
+        if (prev + 1u == ncta) {
+            X.step_ctr[1] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t *>(X.step_ctr) = seq;
+        }
     }
 }
 

@@ -13,7 +13,7 @@ struct CollRank {
 struct CollParams {
     int64_t len;
     int32_t world, gather;
-    uint32_t seq, pad;
+    uint32_t pad0_, pad;
     uint64_t timeout_ns;
     SymLayout lay;
     CollRank r[WS_MAX_WORLD];
@@ -23,7 +23,7 @@ struct CollParams {
 // every peer, releases one flag per CTA and peer, waits for the same CTA of every rank
 // and then adds (rank order 0..R-1, crates/weightstream-transport/src/ring.rs:399-408)
 // or concatenates (ring.rs:426-432) the slots.
-__global__ void __launch_bounds__(256) coll_kernel(const __grid_constant__ CollParams p) {
+__device__ __forceinline__ void coll_body(const CollParams &p, const uint32_t seq) {
     const int vr = blockIdx.y, cta = blockIdx.x, ncta = gridDim.x, tid = threadIdx.x;
     const CollRank &A = p.r[vr];
     const RankCtx &X = A.ctx;
@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(256) coll_kernel(const __grid_constant__ CollP
         for (int64_t i = a + tid; i < b; i += blockDim.x) A.out[i] = A.in[i];
         return;
     }
-    const uint32_t bank = p.seq & 1u;
+    const uint32_t bank = seq & 1u;
     const int nflag = kMaxCtas + kMaxShared;
     const size_t astride = (size_t)p.lay.max_m * p.lay.max_n;
     for (int pr = 0; pr < p.world; ++pr) {
@@ -43,10 +43,10 @@ __global__ void __launch_bounds__(256) coll_kernel(const __grid_constant__ CollP
     __syncthreads();
     if (tid < p.world) {
         uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[tid] + p.lay.flags_off) + ((size_t)bank * p.world + X.rank) * nflag;
-        st_release_sys(f + cta, p.seq);
+        st_release_sys(f + cta, seq);
     }
     const uint32_t *myflags = reinterpret_cast<const uint32_t *>(X.sym[X.rank] + p.lay.flags_off) + (size_t)bank * p.world * nflag;
-    if (tid < p.world) wait_flag(myflags + (size_t)tid * nflag + cta, p.seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
+    if (tid < p.world) wait_flag(myflags + (size_t)tid * nflag + cta, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
     __syncthreads();
     const float *slots = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.slota_off) + (size_t)bank * p.world * astride;
     if (p.gather) {
@@ -59,6 +59,13 @@ __global__ void __launch_bounds__(256) coll_kernel(const __grid_constant__ CollP
             A.out[i] = s;
         }
     }
+}
+
+__global__ void __launch_bounds__(256) coll_kernel(const __grid_constant__ CollParams p) {
+    const RankCtx &X = p.r[blockIdx.y].ctx;
+    const uint32_t seq = step_begin(X);
+    coll_body(p, seq);
+    step_end(X, seq, gridDim.x);
 }
 
 // x [m, k] (bf16 or f32) -> q [m, k] E4M3 bytes, sexp [m, k/32] UE8M0 bytes.

@@ -40,7 +40,7 @@ struct alignas(64) MoeRankArgs {
 
 struct MoeParams {
     int32_t m, n, k, top_k, h_dtype, world, nstages, stage_boxes, split, pad0;
-    uint32_t seq, pad1;
+    uint32_t pad0_, pad1;
     uint64_t timeout_ns;
     SymLayout lay;
     MoeRankArgs r[WS_MAX_WORLD];
@@ -72,7 +72,7 @@ __host__ __device__ inline MoeSmem moe_smem_layout(int nstages, int stage_boxes,
     s.pass_n = o; o += (int)align_up((int64_t)m * top_k, 16);
     s.pass_r = o; o += (int)align_up((int64_t)m * top_k * 8 * 2, 16);
     s.bars = o;   o += 2 * kMaxStages * 8;
-    s.misc = o;   o += 64;
+    s.misc = o;   o += 64 + (kMaxCtas + 8) * 4;
     s.total = o;
     return s;
 }
@@ -88,7 +88,7 @@ __device__ __forceinline__ float e8m0_f32(uint32_t b) {
                         : (b == 0u ? __uint_as_float(0x00400000u) : __uint_as_float(b << 23));
 }
 
-__global__ void __launch_bounds__(kThreads, 1) moe_down_kernel(const __grid_constant__ MoeParams p) {
+__device__ __forceinline__ void moe_down_kernel_body(const MoeParams &p, const uint32_t seq) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     uint8_t *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -186,10 +186,13 @@ __global__ void __launch_bounds__(kThreads, 1) moe_down_kernel(const __grid_cons
 
     // leftover schedule: unit u = (j*NP + pass)*kbox + box
     const int64_t U = p.split ? (int64_t)Rg * NP * kbox : 0;
+    int32_t *ub_s = reinterpret_cast<int32_t *>(smem + S.misc + 64);  // ub_s[c] = first split unit of CTA c
+    for (int c = tid; c <= ncta; c += kThreads) ub_s[c] = (int32_t)unit_begin(c, U, ncta);
+    __syncthreads();
     const int64_t u0 = unit_begin(cta, U, ncta), u1 = unit_begin(cta + 1, U, ncta);
     const int64_t pair0 = (u1 > u0) ? u0 / kbox : 0;
     const int nruns = (u1 > u0) ? (int)((u1 - 1) / kbox - pair0) + 1 : 0;
-    const uint32_t bank = p.seq & 1u;
+    const uint32_t bank = seq & 1u;
     const int nflag = kMaxCtas + kMaxShared;
     const uint32_t scale_item_bytes = (uint32_t)(kGroupRows * kb32);
 
@@ -363,7 +366,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_down_kernel(const __grid_cons
         const int c_lo = owner_of((int64_t)j * NP * kbox, U, ncta);
         const int c_hi = owner_of((int64_t)(j + 1) * NP * kbox - 1, U, ncta);
         uint32_t expect = 0;  // CTAs that hold at least one unit of group j
-        for (int c = c_lo; c <= c_hi; ++c) expect += unit_begin(c + 1, U, ncta) > unit_begin(c, U, ncta) ? 1u : 0u;
+        for (int c = c_lo; c <= c_hi; ++c) expect += ub_s[c + 1] > ub_s[c] ? 1u : 0u;
         if (tid == 0) {
             const uint32_t prev = atomicAdd(X.counters + j, 1u);
             misc_s[0] = (prev + 1u == expect) ? 1u : 0u;
@@ -390,9 +393,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_down_kernel(const __grid_cons
             if (tid < 128 && col_t < pass_n[ps]) {
                 float sum = 0.0f;
                 for (int c = ca; c <= cb; ++c) {
-                    const int64_t cu0 = unit_begin(c, U, ncta);
-                    if (unit_begin(c + 1, U, ncta) == cu0) continue;
-                    const int ridx = (int)(pair - cu0 / kbox);
+                    const int cu0 = ub_s[c];
+                    if (ub_s[c + 1] == cu0) continue;
+                    const int ridx = (int)(pair - (int64_t)((uint32_t)cu0 / (uint32_t)kbox));
                     sum += ld_volatile_f32(X.contrib + ((size_t)c * kMaxRuns + ridx) * (8 * kGroupRows) + tid);
                 }
                 yroute[(size_t)pass_r[ps * 8 + col_t] * kGroupRows + row_t] = sum;
@@ -449,22 +452,22 @@ __global__ void __launch_bounds__(kThreads, 1) moe_down_kernel(const __grid_cons
     if (tid < p.world) {
         uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[tid] + p.lay.flags_off) +
                       ((size_t)bank * p.world + X.rank) * nflag;
-        st_release_sys(f + cta, p.seq);
+        st_release_sys(f + cta, seq);
     }
     if (warp == 1) {
         for (int i = lane; i < nfin * p.world; i += 32) {
             uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[i % p.world] + p.lay.flags_off) +
                           ((size_t)bank * p.world + X.rank) * nflag;
-            st_release_sys(f + kMaxCtas + fin[i / p.world], p.seq);
+            st_release_sys(f + kMaxCtas + fin[i / p.world], seq);
         }
     }
     const uint32_t *myflags = reinterpret_cast<const uint32_t *>(X.sym[X.rank] + p.lay.flags_off) +
                               (size_t)bank * p.world * nflag;
     if (tid < p.world)
-        wait_flag(myflags + (size_t)tid * nflag + cta, p.seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
+        wait_flag(myflags + (size_t)tid * nflag + cta, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
     if (warp == 1)
         for (int i = lane; i < nfin * p.world; i += 32)
-            wait_flag(myflags + (size_t)(i % p.world) * nflag + kMaxCtas + fin[i / p.world], p.seq, p.timeout_ns,
+            wait_flag(myflags + (size_t)(i % p.world) * nflag + kMaxCtas + fin[i / p.world], seq, p.timeout_ns,
                       X.status, kStatTimeoutPeerB);
     consumer_bar();
     const size_t astride = (size_t)p.lay.max_m * p.lay.max_n;
@@ -489,6 +492,13 @@ __global__ void __launch_bounds__(kThreads, 1) moe_down_kernel(const __grid_cons
             A.out[(size_t)tok * p.n + (Gm * ncta + j) * kGroupRows + row_t] = s;
         }
     }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) moe_down_kernel(const __grid_constant__ MoeParams p) {
+    const RankCtx &X = p.r[blockIdx.y].ctx;
+    const uint32_t seq = step_begin(X);
+    moe_down_kernel_body(p, seq);
+    step_end(X, seq, gridDim.x);
 }
 
 }  // namespace ws

@@ -205,7 +205,7 @@ class Endpoint:
         dist.barrier(group=group)
 
     def set_split(self, on: bool) -> None:
-        self._ok(self.lib.ws_tp_set_split(self.handle, 1 if on else 0))
+        self._ok(self.lib.ws_tp_set_split(self.handle, int(on)))
 
     def check(self, stream=None) -> None:
         """Synchronise the stream and raise if a kernel recorded an error (fail-stop)."""
