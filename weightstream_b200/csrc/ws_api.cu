@@ -14,6 +14,7 @@
 #include "../../include/ws_tp.h"
 #include "ws_device.cuh"
 #include "ws_fp8_kernel.cuh"
+#include "ws_fp8_umma_kernel.cuh"
 #include "ws_misc_kernels.cuh"
 #include "ws_moe_kernel.cuh"
 
@@ -34,6 +35,7 @@ struct ws_tp {
     int sm_count = 0, ncta = 0;
     uint64_t timeout_ns = 0;
     int split = 1;
+    int kernel_sel = 0;  // 0: tcgen05 path when the shape allows, 1: always the mma.sync path
     // host-buffer entry points
     cudaStream_t hstream = nullptr;
     void *pin = nullptr;
@@ -217,7 +219,9 @@ ws_status_t ws_tp_create(int32_t world, int32_t rank, int32_t device, const ws_t
     if (cudaDeviceSynchronize() != cudaSuccess) return bail(WS_ERR_CUDA);
     tp->peers[rank] = tp->sym;
     if (world == 1) tp->connected = true;
-    if (set_smem(tp, fp8_rowpar_kernel) != WS_OK || set_smem(tp, moe_down_kernel) != WS_OK) return bail(WS_ERR_CUDA);
+    if (set_smem(tp, fp8_rowpar_kernel) != WS_OK || set_smem(tp, moe_down_kernel) != WS_OK ||
+        set_smem(tp, fp8_umma_kernel) != WS_OK)
+        return bail(WS_ERR_CUDA);
     *out = tp;
     return WS_OK;
 }
@@ -349,11 +353,96 @@ static ws_status_t validate_fp8(ws_tp *tp, const ws_fp8_gemm_args_t &a, bool lm_
     return WS_OK;
 }
 
+// Plan of the tcgen05 path for one fused step; ok = false when the shape does not fit it.
+struct UmmaPlan {
+    bool ok;
+    int chunk_rows, nchunk, pitch, slabs_per_stage, nstages, nslot_max;
+    size_t smem;
+};
+static UmmaPlan umma_plan(int n, int k, int bn, int skb, int ncta) {
+    UmmaPlan u{};
+    const int kslabs = (k + 127) / 128;
+    const int crmax = (n + ncta - 1) / ncta;
+    u.nchunk = (crmax + 127) / 128;
+    u.chunk_rows = (crmax + u.nchunk - 1) / u.nchunk;
+    u.pitch = (u.chunk_rows + 7) / 8 * 8 * 128;
+    u.slabs_per_stage = std::max(1, std::min(8, kStageBytes / u.pitch));
+    u.nslot_max = crmax / bn + 2;
+    const UmmaSmem fixed = umma_smem_layout(0, u.slabs_per_stage, u.pitch, kslabs, u.nslot_max, skb);
+    const int stage_bytes = u.slabs_per_stage * u.pitch;
+    int ns = (kSmemBudget - fixed.total - 1024) / stage_bytes;
+    if (ns > kMaxStages) ns = kMaxStages;
+    u.nstages = ns;
+    u.ok = ns >= 2 && fixed.total < kSmemBudget;
+    if (u.ok) u.smem = (size_t)umma_smem_layout(ns, u.slabs_per_stage, u.pitch, kslabs, u.nslot_max, skb).total + 1024;
+    return u;
+}
+
+// One fused step over at most 8 activation rows on the tcgen05 path.
+static ws_status_t umma_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t *args, const ws_lm_head_args_t *lm,
+                             int m0, int mt, void *const *streams, int ncta, bool same_device, const UmmaPlan &u,
+                             int skb) {
+    ws_tp *t0 = ranks[0];
+    const ws_fp8_gemm_args_t &a0 = lm ? lm[0].g : args[0];
+    UmmaParams p{};
+    p.m = mt; p.n = a0.n; p.k = a0.k; p.x_dtype = a0.x_dtype; p.scale_kind = a0.scale_kind;
+    p.bn = a0.block_n; p.bk = a0.block_k; p.world = t0->world;
+    for (p.bk_shift = 0; (1 << p.bk_shift) < p.bk; ++p.bk_shift) {}
+    for (p.bn_shift = 0; (1 << p.bn_shift) < p.bn; ++p.bn_shift) {}
+    p.mode = lm ? kModeLmHead : kModeAllReduce;
+    p.vocab = lm ? lm[0].vocab : 0;
+    p.chunk_rows = u.chunk_rows; p.nchunk = u.nchunk; p.pitch = u.pitch;
+    p.slabs_per_stage = u.slabs_per_stage; p.nstages = u.nstages; p.nslot_max = u.nslot_max; p.skb = skb;
+    p.timeout_ns = t0->timeout_ns;
+    p.lay = t0->lay;
+    for (int i = 0; i < n; ++i) {
+        ws_tp *t = ranks[i];
+        const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
+        if (lm && lm[i].logits) p.gather_logits = 1;
+        ws_status_t s = make_tmap(t, &p.tmap[i], a.w, (uint64_t)a.n, (uint64_t)a.k, (uint64_t)a.ldw, (uint32_t)u.chunk_rows);
+        if (s != WS_OK) { t0->err = t->err; return s; }
+        Fp8RankArgs &r = p.r[i];
+        const size_t xes = a.x_dtype == WS_ACT_BF16 ? 2 : 4;
+        r.x = static_cast<const char *>(a.x) + (size_t)m0 * a.ldx * xes;
+        r.scales = a.scales;
+        r.out = lm ? nullptr : a.out + (size_t)m0 * a.n;
+        r.logits = lm && lm[i].logits ? lm[i].logits + (size_t)m0 * lm[i].vocab : nullptr;
+        r.argmax = lm && lm[i].argmax ? lm[i].argmax + m0 : nullptr;
+        r.ldx = a.ldx; r.scale_ld = a.scale_ld; r.row0 = a.row0; r.k0 = a.k0;
+        r.vocab_row0 = lm ? lm[i].vocab_row0 : 0;
+        r.ctx = make_ctx(t);
+    }
+    for (int i = 0; i < n; ++i) ranks[i]->step++;
+    if (same_device) {
+        WS_CUDA(t0, cudaSetDevice(t0->device));
+        return launch(t0, fp8_umma_kernel, p, ncta, n, kUmmaThreads, u.smem, static_cast<cudaStream_t>(streams ? streams[0] : nullptr));
+    }
+    for (int i = 0; i < n; ++i) {
+        UmmaParams q = p;
+        q.r[0] = p.r[i];
+        q.tmap[0] = p.tmap[i];
+        WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
+        ws_status_t s = launch(ranks[i], fp8_umma_kernel, q, ncta, 1, kUmmaThreads, u.smem,
+                               static_cast<cudaStream_t>(streams ? streams[i] : nullptr));
+        if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
+    }
+    return WS_OK;
+}
+
 // One fused step over at most 8 activation rows.
 static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t *args, const ws_lm_head_args_t *lm,
                             int m0, int mt, void *const *streams, int ncta, bool same_device) {
     ws_tp *t0 = ranks[0];
     const ws_fp8_gemm_args_t &a0 = lm ? lm[0].g : args[0];
+    if (t0->kernel_sel == 0) {  // tensor-memory path whenever the shape fits it
+        int64_t skb_u = 1;
+        for (int i = 0; i < n; ++i) {
+            const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
+            skb_u = std::max<int64_t>(skb_u, (a.k0 + a.k - 1) / a.block_k - a.k0 / a.block_k + 1);
+        }
+        const UmmaPlan u = umma_plan(a0.n, a0.k, a0.block_n, (int)skb_u, ncta);
+        if (u.ok) return umma_step(ranks, n, args, lm, m0, mt, streams, ncta, same_device, u, (int)skb_u);
+    }
     Fp8Params p{};
     p.m = mt; p.n = a0.n; p.k = a0.k; p.x_dtype = a0.x_dtype; p.scale_kind = a0.scale_kind;
     p.bn = a0.block_n; p.bk = a0.block_k; p.world = t0->world;
@@ -704,6 +793,13 @@ ws_status_t ws_act_quant_fp8(const void *x, int64_t ldx, int32_t x_dtype, int32_
     const unsigned blocks = (unsigned)((total + 255) / 256);
     act_quant_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, ldx, x_dtype, m, k, q, sexp);
     return cudaGetLastError() == cudaSuccess ? WS_OK : WS_ERR_CUDA;
+}
+
+// 0 (default): FP8 steps use the tcgen05 kernel when the shape fits; 1: always the mma.sync kernel.
+ws_status_t ws_tp_set_kernel(ws_tp_t *tp, int32_t which) {
+    if (!tp || which < 0 || which > 1) return WS_ERR_INVALID;
+    tp->kernel_sel = which;
+    return WS_OK;
 }
 
 // Testing knob: 0 makes the leftover row groups whole-CTA work instead of K-split work.

@@ -207,6 +207,10 @@ class Endpoint:
     def set_split(self, on: bool) -> None:
         self._ok(self.lib.ws_tp_set_split(self.handle, int(on)))
 
+    def set_kernel(self, which: int) -> None:
+        """0: tcgen05 kernel when the shape fits (default); 1: always the mma.sync kernel."""
+        self._ok(self.lib.ws_tp_set_kernel(self.handle, int(which)))
+
     def check(self, stream=None) -> None:
         """Synchronise the stream and raise if a kernel recorded an error (fail-stop)."""
         self._ok(self.lib.ws_tp_check(self.handle, _stream_ptr(stream)))
@@ -371,6 +375,10 @@ class LocalGroup:
     def set_split(self, on: bool) -> None:
         for e in self.eps:
             e.set_split(on)
+
+    def set_kernel(self, which: int) -> None:
+        for e in self.eps:
+            e.set_kernel(which)
 
     def check(self) -> None:
         for e in self.eps:
