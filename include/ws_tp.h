@@ -184,8 +184,8 @@ ws_status_t ws_act_quant_fp8(const void *x, int64_t ldx, int32_t x_dtype, int32_
  * row groups that do not divide evenly over the CTAs along K so that every SM streams
  * the same number of bytes; 0 hands each leftover group to one CTA whole. */
 ws_status_t ws_tp_set_split(ws_tp_t *tp, int32_t on);
-/* Kernel choice for the FP8 steps, also without counterpart in the reference: 0 (default) uses
- * the tcgen05 / tensor-memory kernel whenever the shape fits it, 1 always the mma.sync kernel. */
+/* Kernel choice for the FP8 steps, also without counterpart in the reference: 0 (default)
+ * automatic, 1 the mma.sync kernel, 2 the tcgen05 / tensor-memory kernel whenever the shape fits. */
 ws_status_t ws_tp_set_kernel(ws_tp_t *tp, int32_t which);
 
 /* ---- FP8 GEMM for callers that must not allocate ------------------------------------------

@@ -35,7 +35,8 @@ struct ws_tp {
     int sm_count = 0, ncta = 0;
     uint64_t timeout_ns = 0;
     int split = 1;
-    int kernel_sel = 0;  // 0: tcgen05 path when the shape allows, 1: always the mma.sync path
+    int pdl = 1;         // programmatic dependent launch for the FP8 mma.sync kernel
+    int kernel_sel = 0;  // 0: automatic (mma.sync kernel for decode), 1: mma.sync kernel, 2: tcgen05 kernel when the shape fits
     // host-buffer entry points
     cudaStream_t hstream = nullptr;
     void *pin = nullptr;
@@ -130,17 +131,25 @@ ws_status_t set_smem(ws_tp *tp, K kernel) {
 
 template <typename P>
 ws_status_t launch(ws_tp *tp, void (*kernel)(P), const P &params, int ncta, int nvr, int threads, size_t smem,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, bool pdl = false) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)ncta, (unsigned)nvr, 1);
     cfg.blockDim = dim3((unsigned)threads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
-    // Virtual ranks sharing one device wait on one another inside the kernel: they must be
-    // co-resident, which a cooperative launch guarantees (or refuses).
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = nvr > 1 ? 1 : 0;
+    if (nvr > 1) {
+        // Virtual ranks sharing one device wait on one another inside the kernel: they must be
+        // co-resident, which a cooperative launch guarantees (or refuses).
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+    } else {
+        // Programmatic dependent launch: the kernel may start while its predecessor on the stream
+        // is still finishing; it streams (static) weights at once and executes griddepcontrol.wait
+        // before it touches anything the predecessor may have written.
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+    }
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     WS_CUDA(tp, cudaLaunchKernelEx(&cfg, kernel, params));
@@ -366,7 +375,7 @@ static UmmaPlan umma_plan(int n, int k, int bn, int skb, int ncta) {
     u.nchunk = (crmax + 127) / 128;
     u.chunk_rows = (crmax + u.nchunk - 1) / u.nchunk;
     u.pitch = (u.chunk_rows + 7) / 8 * 8 * 128;
-    u.slabs_per_stage = std::max(1, std::min(8, kStageBytes / u.pitch));
+    u.slabs_per_stage = std::max(1, std::min(4, kStageBytes / u.pitch));  // <= 4: a stage's accumulators fill at most half of TMEM
     u.nslot_max = crmax / bn + 2;
     const UmmaSmem fixed = umma_smem_layout(0, u.slabs_per_stage, u.pitch, kslabs, u.nslot_max, skb);
     const int stage_bytes = u.slabs_per_stage * u.pitch;
@@ -434,7 +443,7 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
                             int m0, int mt, void *const *streams, int ncta, bool same_device) {
     ws_tp *t0 = ranks[0];
     const ws_fp8_gemm_args_t &a0 = lm ? lm[0].g : args[0];
-    if (t0->kernel_sel == 0) {  // tensor-memory path whenever the shape fits it
+    if (t0->kernel_sel == 2) {  // tensor-memory path whenever the shape fits it
         int64_t skb_u = 1;
         for (int i = 0; i < n; ++i) {
             const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
@@ -499,7 +508,7 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
     for (int i = 0; i < n; ++i) ranks[i]->step++;
     if (same_device) {
         WS_CUDA(t0, cudaSetDevice(t0->device));
-        return launch(t0, fp8_rowpar_kernel, p, ncta, n, kThreads, smem, static_cast<cudaStream_t>(streams ? streams[0] : nullptr));
+        return launch(t0, fp8_rowpar_kernel, p, ncta, n, kThreads, smem, static_cast<cudaStream_t>(streams ? streams[0] : nullptr), t0->pdl != 0);
     }
     for (int i = 0; i < n; ++i) {  // one launch per device, each sees itself as virtual rank 0
         Fp8Params q = p;
@@ -508,7 +517,7 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
         q.tmap[0][1] = p.tmap[i][1];
         WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
         ws_status_t s = launch(ranks[i], fp8_rowpar_kernel, q, ncta, 1, kThreads, smem,
-                               static_cast<cudaStream_t>(streams ? streams[i] : nullptr));
+                               static_cast<cudaStream_t>(streams ? streams[i] : nullptr), t0->pdl != 0);
         if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
     }
     return WS_OK;
@@ -795,9 +804,9 @@ ws_status_t ws_act_quant_fp8(const void *x, int64_t ldx, int32_t x_dtype, int32_
     return cudaGetLastError() == cudaSuccess ? WS_OK : WS_ERR_CUDA;
 }
 
-// 0 (default): FP8 steps use the tcgen05 kernel when the shape fits; 1: always the mma.sync kernel.
+// 0 (default): automatic; 1: the mma.sync kernel; 2: the tcgen05 kernel when the shape fits.
 ws_status_t ws_tp_set_kernel(ws_tp_t *tp, int32_t which) {
-    if (!tp || which < 0 || which > 1) return WS_ERR_INVALID;
+    if (!tp || which < 0 || which > 2) return WS_ERR_INVALID;
     tp->kernel_sel = which;
     return WS_OK;
 }
@@ -806,6 +815,8 @@ ws_status_t ws_tp_set_kernel(ws_tp_t *tp, int32_t which) {
 ws_status_t ws_tp_set_split(ws_tp_t *tp, int32_t on) {
     if (!tp) return WS_ERR_INVALID;
     tp->split = on < 0 ? 0 : (on > 2 ? 2 : on);
+    tp->pdl = (on & 4) ? 0 : 1;  // bit 2 switches programmatic dependent launch off (measurement aid)
+    tp->split &= 3;
     return WS_OK;
 }
 
@@ -918,6 +929,7 @@ ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *a, int32_t devi
 
 #ifdef WS_TRACE
 void ws_debug_read_trace(unsigned long long *out) { cudaMemcpyFromSymbol(out, g_ws_trace, sizeof(g_ws_trace)); }
+void ws_debug_read_trace2(unsigned long long *out) { cudaMemcpyFromSymbol(out, g_ws_trace2, sizeof(g_ws_trace2)); }
 #endif
 
 }  // extern "C"

@@ -105,11 +105,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~2^27 probes (seconds), records why, and lets the
+// Bounded wait: gives up after two seconds of wall time (globaltimer), records why, and lets the
 // caller unwind instead of spinning forever.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *status) {
-    for (uint32_t i = 0; i < (1u << 27); ++i) {
+    for (int i = 0; i < 64; ++i)
         if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (globaltimer_ns() - t0 > 2000000000ull) break;
     }
     atomicCAS(status, 0u, kStatTimeoutTma | (uint32_t)(-WS_ERR_TIMEOUT));
     return false;

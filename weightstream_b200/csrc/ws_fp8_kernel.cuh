@@ -29,8 +29,13 @@ enum { kModeAllReduce = 0, kModeLmHead = 1 };
 #ifdef WS_TRACE  // phase timestamps per CTA, for a probe build only
 __device__ unsigned long long g_ws_trace[kMaxCtas][8];
 #define WS_MARK(i) do { if (threadIdx.x == 0) g_ws_trace[blockIdx.x][i] = globaltimer_ns(); } while (0)
+#define WS_MARK_T(i, t) do { if (threadIdx.x == (t)) g_ws_trace[blockIdx.x][i] = globaltimer_ns(); } while (0)
+__device__ unsigned long long g_ws_trace2[256];  // fine-grained marks of CTA 0
+#define WS_MARK2(i) do { if (blockIdx.x == 0 && (i) < 256) g_ws_trace2[i] = globaltimer_ns(); } while (0)
 #else
+#define WS_MARK2(i) do { } while (0)
 #define WS_MARK(i) do { } while (0)
+#define WS_MARK_T(i, t) do { } while (0)
 #endif
 
 struct Fp8RankArgs {
@@ -115,7 +120,7 @@ __device__ __forceinline__ bool cand_better(float v, uint32_t i, float bv, uint3
     return v > bv || (v == bv && i < bi);
 }
 
-__device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p, const uint32_t seq) {
+__device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     uint8_t *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -160,8 +165,9 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p, const
     }
     __syncthreads();
 
-    const uint32_t bank = seq & 1u;
     const int nflag = kMaxCtas + kMaxShared;
+    // Let the next kernel on the stream begin (it only prefetches weights until its own wait).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------ TMA producer warp
@@ -192,6 +198,12 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p, const
     }
 
     // ---------------------------------------------------------------- consumer warps
+    // Everything below may read what the previous kernel on the stream wrote (activations, the
+    // step sequence, exchange slots): wait for it.  The producer warp above streams weights,
+    // which are static, and does not wait.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t seq = step_begin(X);
+    const uint32_t bank = seq & 1u;
     // Prologue: weight scales of the rows this CTA touches (loads issued first, stored last, so
     // their latency overlaps the activation loads), then the activation quantisation.
     // q_s[kb][tok][32] holds E4M3 bytes, sa_s[kb][tok(8)] the block scale 2^e.
@@ -474,9 +486,11 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p, const
 
 __global__ void __launch_bounds__(kThreads, 1) fp8_rowpar_kernel(const __grid_constant__ Fp8Params p) {
     const RankCtx &X = p.r[blockIdx.y].ctx;
-    const uint32_t seq = step_begin(X);
-    fp8_rowpar_kernel_body(p, seq);
-    if (p.world > 1 || p.mode == kModeLmHead) step_end(X, seq, gridDim.x);  // a lone all-reduce rank exchanges nothing
+    fp8_rowpar_kernel_body(p);
+    if (p.world > 1 || p.mode == kModeLmHead) {  // a lone all-reduce rank exchanges nothing
+        // step_begin again: the value is unchanged until the last CTA publishes the next one below
+        step_end(X, step_begin(X), gridDim.x);
+    }
 }
 
 }  // namespace ws

@@ -29,9 +29,9 @@
 namespace ws {
 
 constexpr int kUmmaThreads = 192;   // warp 0: TMA, warp 1: MMA issue + TMEM owner, warps 2-5: epilogue
-constexpr int kUmmaBufs = 4;        // TMEM accumulator buffers (one slab each)
-constexpr int kUmmaBufCols = 64;    // 4 K-blocks x 16 MMA columns
-constexpr int kUmmaTmemCols = kUmmaBufs * kUmmaBufCols;
+constexpr int kUmmaSlabCols = 64;   // TMEM columns one slab needs: 4 K-blocks x 16 MMA columns
+constexpr int kUmmaTmemCols = 512;  // all of it: a TMEM buffer holds the accumulators of one whole stage
+constexpr int kUmmaMaxBufs = 8;
 
 struct alignas(64) UmmaParams {
     CUtensorMap tmap[WS_MAX_WORLD];  // per rank: weight shard [n][k bytes], box 128 bytes x chunk_rows, 128B swizzle
@@ -58,7 +58,7 @@ __host__ __device__ inline UmmaSmem umma_smem_layout(int nstages, int slabs_per_
     if (kslabs * 1024 < 16384) o += 16384 - kslabs * 1024;
     s.sa = o;     o += kslabs * 4 * 8 * 4;
     s.sw = o;     o += (int)align_up((int64_t)nslot_max * skb * 4, 16);
-    s.bars = o;   o += (2 * kMaxStages + 2 * kUmmaBufs) * 8;
+    s.bars = o;   o += (2 * kMaxStages + kUmmaMaxBufs) * 8;
     s.misc = o;   o += 64 + 4 * 8 * 8;             // TMEM base, per-warp argmax candidates
     s.total = o;
     return s;
@@ -87,15 +87,23 @@ __device__ __forceinline__ void umma_f8_ss(uint32_t tmem_d, uint64_t adesc, uint
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0u), "r"(0u)
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&d)[8]) {
-    uint32_t r[8];
+// Issue (do not wait for) the load of 8 consecutive columns of this warp's 32 TMEM lanes.
+__device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, uint32_t (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr)
                  : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 8; ++i) d[i] = __uint_as_float(r[i]);
+}
+// Wait for every TMEM load issued so far.  The registers pass through the statement so that no
+// use of them can be scheduled before the wait.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
 }
 // Shared-memory matrix descriptor: K-major, 128B swizzle, 8-row groups `sbo` bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t sbo) {
@@ -139,19 +147,21 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
     float *sw_s = reinterpret_cast<float *>(smem + S.sw);
     uint32_t *misc_s = reinterpret_cast<uint32_t *>(smem + S.misc);
     const uint32_t stage0 = smem_u32(smem + S.stages);
-    const uint32_t full0 = smem_u32(smem + S.bars), empty0 = full0 + kMaxStages * 8;
-    const uint32_t tfull0 = empty0 + kMaxStages * 8, tempty0 = tfull0 + kUmmaBufs * 8;
+    // full[s]: the stage's TMA bytes landed.  done[s]: every MMA of the stage completed (ONE
+    // tcgen05.commit per stage) -- the producer reads it as "stage free", the epilogue as
+    // "accumulators ready".  tempty[b]: TMEM buffer b has been drained.
+    const uint32_t full0 = smem_u32(smem + S.bars), done0 = full0 + kMaxStages * 8;
+    const uint32_t tempty0 = done0 + kMaxStages * 8;
+    const int NB = kUmmaTmemCols / (SL * kUmmaSlabCols);  // TMEM buffers (host keeps SL <= 4, so NB >= 2)
     const uint32_t stage_bytes = (uint32_t)(SL * p.pitch);
+    WS_MARK(0);
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(full0 + s * 8, 1);
-            mbar_init(empty0 + s * 8, 1);
+            mbar_init(done0 + s * 8, 1);
         }
-        for (int b = 0; b < kUmmaBufs; ++b) {
-            mbar_init(tfull0 + b * 8, 1);
-            mbar_init(tempty0 + b * 8, 4);  // one arrival per epilogue warp
-        }
+        for (int b = 0; b < kUmmaMaxBufs; ++b) mbar_init(tempty0 + b * 8, 4);  // one arrival per epilogue warp
         mbar_fence_init();
     }
     if (warp == 1) {  // TMEM: allocated and freed by the same warp
@@ -174,7 +184,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
                 for (int s0 = 0; s0 < kslabs; s0 += SL) {
                     const int nsl = min(SL, kslabs - s0);
                     const int s = item % NS;
-                    mbar_wait(empty0 + s * 8, (((uint32_t)(item / NS)) & 1u) ^ 1u, X.status);
+                    mbar_wait(done0 + s * 8, (((uint32_t)(item / NS)) & 1u) ^ 1u, X.status);
                     mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)(nsl * p.chunk_rows * 128));
                     for (int j = 0; j < nsl; ++j)
                         tma_load_2d(stage0 + s * stage_bytes + j * p.pitch, &p.tmap[vr], (s0 + j) * 128, r0, full0 + s * 8);
@@ -238,31 +248,33 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA
         quant_bar();
+        WS_MARK_T(1, 32);
 
         if (warp == 1) {
             // -------------------------------------------------------- MMA issue (one thread)
             if (lane == 0) {
-                int item = 0, it = 0;
+                int item = 0;
                 for (int c = 0; c < p.nchunk; ++c) {
-                    for (int s0 = 0; s0 < kslabs; s0 += SL) {
+                    for (int s0 = 0; s0 < kslabs; s0 += SL, ++item) {
                         const int nsl = min(SL, kslabs - s0);
-                        const int s = item % NS;
+                        const int s = item % NS, tb = item % NB;
+                        WS_MARK2(item * 4 + 0);
+                        mbar_wait(tempty0 + tb * 8, (((uint32_t)(item / NB)) & 1u) ^ 1u, X.status);
                         mbar_wait(full0 + s * 8, ((uint32_t)(item / NS)) & 1u, X.status);
                         tc_fence_after();
-                        for (int j = 0; j < nsl; ++j, ++it) {
-                            const int slab = s0 + j, buf = it % kUmmaBufs;
-                            mbar_wait(tempty0 + buf * 8, (((uint32_t)(it / kUmmaBufs)) & 1u) ^ 1u, X.status);
-                            tc_fence_after();
+                        WS_MARK2(item * 4 + 1);
+                        for (int j = 0; j < nsl; ++j) {
+                            const int slab = s0 + j;
                             const uint32_t a_addr = stage0 + s * stage_bytes + j * p.pitch;
                             const uint32_t b_addr = smem_u32(q_s) + slab * 1024;
                             const int nblk = min(4, kb32 - slab * 4);
                             for (int b = 0; b < nblk; ++b)
-                                umma_f8_ss(tmem_base + buf * kUmmaBufCols + b * 16, umma_desc(a_addr + b * 32, 1024),
-                                           umma_desc(b_addr + b * 32, 0), kUmmaIdesc);
-                            umma_commit(tfull0 + buf * 8);  // accumulators of this slab are complete
+                                umma_f8_ss(tmem_base + (tb * SL + j) * kUmmaSlabCols + b * 16,
+                                           umma_desc(a_addr + b * 32, 1024), umma_desc(b_addr + b * 32, 0), kUmmaIdesc);
                         }
-                        umma_commit(empty0 + s * 8);        // the stage's bytes have been consumed
-                        ++item;
+                        WS_MARK2(item * 4 + 2);
+                        umma_commit(done0 + s * 8);  // stage consumed and its accumulators complete
+                        WS_MARK2(item * 4 + 3);
                     }
                 }
             }
@@ -280,37 +292,79 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
             uint32_t cbi[8];
 #pragma unroll
             for (int t = 0; t < 8; ++t) { cbv[t] = -INFINITY; cbi[t] = 0xFFFFFFFFu; }
-            int it = 0;
+            int item0 = 0;  // first stage item of the current chunk
             for (int c = 0; c < p.nchunk; ++c) {
                 const int row = row_a + c * p.chunk_rows + rc;
                 const bool mine = rc < p.chunk_rows && row < row_b;
                 const float *swrow = sw_s + (mine ? (int)(((A.row0 + row) >> p.bn_shift) - srow_lo) : 0) * p.skb;
                 float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                for (int slab = 0; slab < kslabs; ++slab, ++it) {
-                    const int buf = it % kUmmaBufs;
-                    mbar_wait(tfull0 + buf * 8, ((uint32_t)(it / kUmmaBufs)) & 1u, X.status);
-                    tc_fence_after();
+                // Drain one slab: its four K blocks are loaded with one wait, and the loads of the
+                // next slab are in flight while this slab's products are added.
+                uint32_t cur[32], nxt[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) cur[i] = nxt[i] = 0u;
+                // slab `sl` of this chunk lives in stage item (item0 + sl / SL), TMEM buffer item % NB
+                auto issue_slab = [&](int sl, uint32_t (&r)[32]) {
+                    const int item = item0 + sl / SL, j = sl % SL;
+                    if (j == 0) {
+                        mbar_wait(done0 + (item % NS) * 8, ((uint32_t)(item / NS)) & 1u, X.status);
+                        tc_fence_after();
+                        if (tid == 64) WS_MARK2(128 + item * 2);
+                    }
+                    const int nblk = min(4, kb32 - sl * 4);
+                    const uint32_t col = tlane + ((item % NB) * SL + j) * kUmmaSlabCols;
+#pragma unroll
+                    for (int b = 0; b < 4; ++b)
+                        if (b < nblk) tmem_ld8_issue(col + b * 16, *reinterpret_cast<uint32_t (*)[8]>(&r[b * 8]));
+                };
+                auto loaded_slab = [&](int sl) {  // after the wait: the last slab of a stage frees its TMEM buffer
+                    if ((sl % SL) == SL - 1 || sl == kslabs - 1) {
+                        if (tid == 64) WS_MARK2(128 + (item0 + sl / SL) * 2 + 1);
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty0 + ((item0 + sl / SL) % NB) * 8);
+                    }
+                };
+                auto add_slab = [&](int slab, const uint32_t (&r)[32]) {
                     const int nblk = min(4, kb32 - slab * 4);
-                    for (int b = 0; b < nblk; ++b) {
-                        float d[8];
-                        tmem_ld8(tlane + buf * kUmmaBufCols + b * 16, d);
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        if (b >= nblk) break;
                         const int kb = slab * 4 + b;
                         const float sw = swrow[(kofs + kb * 32) >> p.bk_shift];
                         const float4 s0 = *reinterpret_cast<const float4 *>(sa_s + kb * 8);
                         const float4 s1 = *reinterpret_cast<const float4 *>(sa_s + kb * 8 + 4);
-                        acc[0] = fmaf(d[0], s0.x * sw, acc[0]);
-                        acc[1] = fmaf(d[1], s0.y * sw, acc[1]);
-                        acc[2] = fmaf(d[2], s0.z * sw, acc[2]);
-                        acc[3] = fmaf(d[3], s0.w * sw, acc[3]);
-                        acc[4] = fmaf(d[4], s1.x * sw, acc[4]);
-                        acc[5] = fmaf(d[5], s1.y * sw, acc[5]);
-                        acc[6] = fmaf(d[6], s1.z * sw, acc[6]);
-                        acc[7] = fmaf(d[7], s1.w * sw, acc[7]);
+                        acc[0] = fmaf(__uint_as_float(r[b * 8 + 0]), s0.x * sw, acc[0]);
+                        acc[1] = fmaf(__uint_as_float(r[b * 8 + 1]), s0.y * sw, acc[1]);
+                        acc[2] = fmaf(__uint_as_float(r[b * 8 + 2]), s0.z * sw, acc[2]);
+                        acc[3] = fmaf(__uint_as_float(r[b * 8 + 3]), s0.w * sw, acc[3]);
+                        acc[4] = fmaf(__uint_as_float(r[b * 8 + 4]), s1.x * sw, acc[4]);
+                        acc[5] = fmaf(__uint_as_float(r[b * 8 + 5]), s1.y * sw, acc[5]);
+                        acc[6] = fmaf(__uint_as_float(r[b * 8 + 6]), s1.z * sw, acc[6]);
+                        acc[7] = fmaf(__uint_as_float(r[b * 8 + 7]), s1.w * sw, acc[7]);
                     }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty0 + buf * 8);
+                };
+                issue_slab(0, cur);
+                tmem_ld_wait(cur);
+                loaded_slab(0);
+                if (c == 0) WS_MARK_T(4, 64);
+                for (int slab = 0; slab < kslabs; slab += 2) {
+                    // cur holds slab; fetch slab+1 into nxt while adding cur, then the other way round
+                    if (slab + 1 < kslabs) issue_slab(slab + 1, nxt);
+                    add_slab(slab, cur);
+                    if (slab + 1 < kslabs) {
+                        tmem_ld_wait(nxt);
+                        loaded_slab(slab + 1);
+                        if (slab + 2 < kslabs) issue_slab(slab + 2, cur);
+                        add_slab(slab + 1, nxt);
+                        if (slab + 2 < kslabs) {
+                            tmem_ld_wait(cur);
+                            loaded_slab(slab + 2);
+                        }
+                    }
                 }
+                item0 += (kslabs + SL - 1) / SL;
+                WS_MARK_T(2, 64);
                 // publish this chunk's rows
                 if (mine) {
                     if (solo) {
@@ -446,6 +500,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
         }
     }
 
+    WS_MARK_T(5, 64);
+    WS_MARK_T(3, 64);
     // ---- teardown: every TMEM read and MMA has completed once all threads are here
     tc_fence_before();
     __syncthreads();

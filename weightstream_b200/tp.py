@@ -208,7 +208,7 @@ class Endpoint:
         self._ok(self.lib.ws_tp_set_split(self.handle, int(on)))
 
     def set_kernel(self, which: int) -> None:
-        """0: tcgen05 kernel when the shape fits (default); 1: always the mma.sync kernel."""
+        """0: automatic (default); 1: the mma.sync kernel; 2: the tcgen05 kernel when the shape fits."""
         self._ok(self.lib.ws_tp_set_kernel(self.handle, int(which)))
 
     def check(self, stream=None) -> None:
