@@ -624,42 +624,51 @@ ws_status_t ws_moe_down_combine_allreduce_group(ws_tp_t *const *ranks, int32_t n
     p.m = a0.m; p.n = a0.n; p.k = a0.k; p.top_k = a0.top_k; p.h_dtype = a0.h_dtype; p.world = t0->world;
     p.timeout_ns = t0->timeout_ns;
     p.lay = t0->lay;
-    const int kbox = (p.k / 2 + 127) / 128;
-    p.stage_boxes = std::min(kbox, kBoxesPerStage);
-    const int G = p.n / kGroupRows, Gm = G / ncta, Rg = G - Gm * ncta;
-    p.split = t0->split;
-    // the split schedule gives one CTA at most ceil(Rg*routes/ncta)+1 (group, pass) runs
-    if (p.split && ((int64_t)Rg * p.m * p.top_k + ncta - 1) / ncta + 2 > kMaxRuns) p.split = 0;
-    const int owned_rows = (Gm + ((!p.split && Rg) ? 1 : 0)) * kGroupRows;
+    const int kbox = (p.k / 2 + 127) / 128, kb32 = p.k / 32;
+    p.tiles_per_item = kbox * kBoxBytes <= kStageBytes / 2 ? 2 : 1;  // keep a stage near 32 KB
+    const int Gm = p.n / kGroupRows / ncta;
+    p.ragged = (t0->split && Gm < 8) ? 1 : 0;
+    p.gran = ragged_granularity(p.n, ncta);
+    // the rows' scale bytes travel by bulk copy: sizes and addresses must be multiples of 16 bytes
+    while (p.gran < kGroupRows && (p.gran * kb32) % 16) p.gran *= 2;
+    if (p.gran >= kGroupRows) { p.ragged = 0; p.gran = 1; }
+    p.part_rows = (Gm + 2) * kGroupRows;
     int e_len_max = 0;
     for (int i = 0; i < n; ++i) e_len_max = std::max(e_len_max, args[i].e_len);
-    const MoeSmem fixed = moe_smem_layout(0, p.stage_boxes, p.k, p.m, p.top_k, e_len_max, owned_rows);
+    const MoeSmem fixed = moe_smem_layout(0, p.tiles_per_item, p.k, p.m, p.top_k, e_len_max, p.part_rows);
     int ns = (kSmemBudget - fixed.total) / fixed.stage_bytes;
     if (ns > kMaxStages) ns = kMaxStages;
     if (ns < 2)
         return fail(t0, WS_ERR_CAPACITY, "shapes m=%d n=%d k=%d leave no room for the weight stage ring", p.m, p.n, p.k);
     p.nstages = ns;
-    const size_t smem = (size_t)moe_smem_layout(ns, p.stage_boxes, p.k, p.m, p.top_k, e_len_max, owned_rows).total + 1024;
+    const size_t smem = (size_t)moe_smem_layout(ns, p.tiles_per_item, p.k, p.m, p.top_k, e_len_max, p.part_rows).total + 1024;
     for (int i = 0; i < n; ++i) {
         const ws_moe_down_args_t &a = args[i];
-        MoeRankArgs &r = p.r[i];
-        s = make_tmap(ranks[i], &r.tmap, a.w2, (uint64_t)a.e_len * a.n, (uint64_t)a.k / 2, (uint64_t)a.k / 2);
-        if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
-        r.h = a.h; r.route_ids = a.route_ids; r.route_w = a.route_w; r.s2 = a.s2; r.out = a.out;
-        r.ldh = a.ldh; r.e_start = a.e_start; r.e_len = e_len_max == a.e_len ? a.e_len : a.e_len;
-        r.ctx = make_ctx(ranks[i]);
         if (a.e_len != e_len_max) return fail(t0, WS_ERR_INVALID, "ranks must hold equally many experts");
+        for (int b = 0; b < 2; ++b) {
+            s = make_tmap(ranks[i], &p.tmap[i][b], a.w2, (uint64_t)a.e_len * a.n, (uint64_t)a.k / 2, (uint64_t)a.k / 2,
+                          b ? (uint32_t)p.gran : (uint32_t)kGroupRows);
+            if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
+        }
+        MoeRankArgs &r = p.r[i];
+        r.h = a.h; r.route_ids = a.route_ids; r.route_w = a.route_w; r.s2 = a.s2; r.out = a.out;
+        r.ldh = a.ldh; r.e_start = a.e_start; r.e_len = a.e_len;
+        r.ctx = make_ctx(ranks[i]);
     }
     for (int i = 0; i < n; ++i) ranks[i]->step++;
     if (same) {
         WS_CUDA(t0, cudaSetDevice(t0->device));
-        return launch(t0, moe_down_kernel, p, ncta, n, kThreads, smem, static_cast<cudaStream_t>(streams ? streams[0] : nullptr));
+        return launch(t0, moe_down_kernel, p, ncta, n, kThreads, smem, static_cast<cudaStream_t>(streams ? streams[0] : nullptr),
+                      t0->pdl != 0);
     }
     for (int i = 0; i < n; ++i) {
         MoeParams q = p;
         q.r[0] = p.r[i];
+        q.tmap[0][0] = p.tmap[i][0];
+        q.tmap[0][1] = p.tmap[i][1];
         WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
-        s = launch(ranks[i], moe_down_kernel, q, ncta, 1, kThreads, smem, static_cast<cudaStream_t>(streams ? streams[i] : nullptr));
+        s = launch(ranks[i], moe_down_kernel, q, ncta, 1, kThreads, smem, static_cast<cudaStream_t>(streams ? streams[i] : nullptr),
+                   t0->pdl != 0);
         if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
     }
     return WS_OK;

@@ -17,7 +17,7 @@ constexpr int kThreads = kConsumerThreads + 32;  // + one TMA producer warp
 constexpr int kBoxBytes = 2048;                  // one TMA box: 16 rows x 128 bytes
 constexpr int kBoxesPerStage = 16;
 constexpr int kStageBytes = kBoxBytes * kBoxesPerStage;  // 32 KB
-constexpr int kMaxStages = 6;
+constexpr int kMaxStages = 12;
 constexpr int kMaxCtas = 160;    // persistent CTAs per rank (one per SM on B200: 148)
 constexpr int kMaxShared = 160;  // output row groups whose K range is split across CTAs
 constexpr int kMaxRuns = 16;     // split contributions one CTA may produce
