@@ -201,9 +201,11 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     // Everything below may read what the previous kernel on the stream wrote (activations, the
     // step sequence, exchange slots): wait for it.  The producer warp above streams weights,
     // which are static, and does not wait.
+    if (tid == 0) WS_MARK2(0);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t seq = step_begin(X);
     const uint32_t bank = seq & 1u;
+    if (tid == 0) WS_MARK2(1);
     // Prologue: weight scales of the rows this CTA touches (loads issued first, stored last, so
     // their latency overlaps the activation loads), then the activation quantisation.
     // q_s[kb][tok][32] holds E4M3 bytes, sa_s[kb][tok(8)] the block scale 2^e.
@@ -234,8 +236,10 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
             const int i = tid + u * kConsumerThreads;
             pre[u] = i < nsw ? load_scale(i) : 0.0f;
         }
-        for (int i = tid; i < kbox * 4 * (8 - p.mp); i += kConsumerThreads)  // tokens the launch does not carry
-            sa_s[(i / (8 - p.mp)) * 8 + p.mp + i % (8 - p.mp)] = 0.0f;
+        if (tid == 0) WS_MARK2(2);
+        for (int i = tid; i < kbox * 4 * 8; i += kConsumerThreads)  // tokens the launch does not carry
+            if ((i & 7) >= p.mp) sa_s[i] = 0.0f;
+        if (tid == 0) WS_MARK2(3);
         const int chunks_per_row = kbox * 16;  // 8-element chunks over the padded K
         const int total = p.mp * chunks_per_row;
         // four chunks per thread and pass: all loads are in flight before the first is used
@@ -266,6 +270,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
                 }
             }
         }
+        if (tid == 0) WS_MARK2(4);
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int i = tid + u * kConsumerThreads;
@@ -273,7 +278,9 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         }
         for (int i = tid + 4 * kConsumerThreads; i < nsw; i += kConsumerThreads) sw_s[sw_index(i)] = load_scale(i);
     }
+    if (tid == 0) WS_MARK2(5);
     consumer_bar();
+    if (tid == 0) WS_MARK2(6);
     WS_MARK(1);
 
     const int g = lane >> 2, tq = lane & 3;
@@ -388,8 +395,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
             float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
             for_rows([&](int tok, int row, int pi) { dst[(size_t)tok * p.n + row] = part_s[pi]; });
         }
-        __threadfence_system();
-        consumer_bar();
+        consumer_bar();  // the st.release.sys below is cumulative over the stores this barrier ordered
         if (tid < p.world) {
             uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[tid] + p.lay.flags_off) +
                           ((size_t)bank * p.world + X.rank) * nflag;
@@ -439,8 +445,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
             *dst = ((uint64_t)__float_as_uint(bv) << 32) | bi;
         }
     }
-    __threadfence_system();
-    consumer_bar();
+    consumer_bar();  // the st.release.sys below is cumulative over the stores this barrier ordered
     if (tid < p.world) {
         uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[tid] + p.lay.flags_off) +
                       ((size_t)bank * p.world + X.rank) * nflag;

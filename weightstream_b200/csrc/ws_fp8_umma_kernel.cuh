@@ -402,8 +402,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
                                            : reinterpret_cast<const uint32_t *>(X.sym[X.rank] + p.lay.flags_off) +
                                                  (size_t)bank * p.world * nflag;
             if (!solo && p.mode == kModeAllReduce) {
-                __threadfence_system();
-                epi_bar();
+                epi_bar();  // the st.release.sys below is cumulative over the stores this barrier ordered
                 if (et < p.world) {
                     uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[et] + p.lay.flags_off) +
                                   ((size_t)bank * p.world + X.rank) * nflag;
@@ -451,8 +450,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
                         *dst = ((uint64_t)__float_as_uint(bv) << 32) | bi;
                     }
                 }
-                __threadfence_system();
-                epi_bar();
+                epi_bar();  // the st.release.sys below is cumulative over the stores this barrier ordered
                 if (et < p.world) {
                     uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[et] + p.lay.flags_off) +
                                   ((size_t)bank * p.world + X.rank) * nflag;

@@ -39,8 +39,7 @@ __device__ __forceinline__ void coll_body(const CollParams &p, const uint32_t se
         float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
         for (int64_t i = a + tid; i < b; i += blockDim.x) dst[i] = A.in[i];
     }
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();  // the st.release.sys below is cumulative over the stores this barrier ordered
     if (tid < p.world) {
         uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[tid] + p.lay.flags_off) + ((size_t)bank * p.world + X.rank) * nflag;
         st_release_sys(f + cta, seq);

@@ -397,8 +397,7 @@ __device__ __forceinline__ void moe_down_body(const MoeParams &p) {
         float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
         for_rows([&](int tok, int row, int pi) { dst[(size_t)tok * p.n + row] = part_s[pi]; });
     }
-    __threadfence_system();
-    consumer_bar();
+    consumer_bar();  // the st.release.sys below is cumulative over the stores this barrier ordered
     if (tid < p.world) {
         uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[tid] + p.lay.flags_off) + ((size_t)bank * p.world + X.rank) * nflag;
         st_release_sys(f + cta, seq);
