@@ -155,6 +155,105 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def build_workload(args, tp, synth, torch, dev, sh, l2_bytes):
+    """Returns (step(i), e2e_step(i) or None, algorithmic bytes per launch on this rank, config dict,
+    h2d bytes, d2h bytes, endpoint)."""
+    world, rank, m, wl = sh.world_size, sh.rank, args.m, args.workload
+    g = torch.Generator(device=dev)
+    g.manual_seed(99)
+    if wl in ("o_proj", "shared_down"):
+        k_full = K_FULL if wl == "o_proj" else 2048
+        k0, kl = sh.slice_of(k_full)
+        per_set = N_OUT * kl
+        layers = min(64, max(4, int(np.ceil(3.0 * l2_bytes / per_set))))
+        ep = tp.Endpoint(sh, dev.index, max_m=max(m, 8), max_n=N_OUT, wait_ms=5000)
+        ws, scs = [], []
+        for l in range(layers):  # every rank quantises the SAME full tensors (same seed) and keeps its K slice
+            w, sc = synth.torch_fp8_weight(N_OUT, k_full, seed=synth.config_seed(wl, m, 1) + l, device=dev)
+            ws.append(w[:, k0:k0 + kl].contiguous())
+            scs.append(sc)
+            del w
+        x = torch.randn((m, k_full), generator=g, device=dev).to(torch.bfloat16)[:, k0:k0 + kl].contiguous()
+        outs = [torch.empty((m, N_OUT), dtype=torch.float32, device=dev) for _ in range(2)]
+        x_host = x.view(torch.int16).cpu().numpy().view(np.uint16)
+
+        def step(i):
+            ep.fp8_rowpar_gemm_allreduce(x, ws[i % layers], scs[i % layers], block=(BN, BK), k0=k0, out=outs[i & 1])
+
+        def e2e(i):
+            ep.fp8_rowpar_gemm_allreduce_host(x_host, ws[i % layers], scs[i % layers], block=(BN, BK), k0=k0)
+
+        cfg = {"workload": f"{wl} fp8 [{N_OUT}x{k_full}] K/{world} per rank + fused fp32 all-reduce, M={m}",
+               "m": m, "n": N_OUT, "k": k_full, "k_per_rank": kl, "parallelism": f"tp{world}",
+               "l2": f"{layers} rotating weight sets ({layers * per_set / 1e6:.0f} MB per rank) > {l2_bytes / 1e6:.0f} MB L2; no flush needed"}
+        return step, e2e, algorithmic_bytes(m, N_OUT, kl), cfg, m * kl * 2, m * N_OUT * 4, ep
+    if wl == "lm_head":
+        vocab, k = 129280, 7168
+        v0, vl = sh.slice_of(vocab)
+        ep = tp.Endpoint(sh, dev.index, max_m=8, max_n=16, max_vocab=vocab, wait_ms=5000)
+        # one weight set: a vocab shard is far larger than L2 at every N (116 MB at N=8 is borderline: two sets there)
+        sets = 2 if vl * k < 2 * l2_bytes else 1
+        ws, scs, row0 = [], [], 0
+        for l in range(sets):
+            w, sc = synth.torch_fp8_weight(vocab, k, seed=synth.config_seed(wl, m, 1) + l, device=dev)
+            s_r, row0, _ = tp.shard_scale(sc, sc.shape, tp.WShard.Rows(v0, vl), block=(BN, BK))
+            ws.append(w[v0:v0 + vl].contiguous())
+            scs.append(s_r.contiguous())
+            del w
+        x = torch.randn((m, k), generator=g, device=dev).to(torch.bfloat16)
+        x_pin = x.cpu().pin_memory()
+        arg_pin = torch.empty((m,), dtype=torch.int32).pin_memory()
+        xd = torch.empty_like(x)
+
+        def step(i):
+            ep.lm_head_allgather_argmax(x, ws[i % sets], scs[i % sets], vocab_row0=v0, vocab=vocab, row0=row0,
+                                        want_logits=False)
+
+        def e2e(i):
+            xd.copy_(x_pin, non_blocking=True)
+            _, am = ep.lm_head_allgather_argmax(xd, ws[i % sets], scs[i % sets], vocab_row0=v0, vocab=vocab,
+                                                row0=row0, want_logits=False)
+            arg_pin.copy_(am, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        ab = vl * k + (-(-vl // BN) + 1) * (k // BK) * 4 + m * k * 2 + m * 4
+        cfg = {"workload": f"lm_head fp8 [{vocab}x{k}] vocab/{world} per rank + argmax candidates gathered, M={m}",
+               "m": m, "vocab": vocab, "k": k, "rows_per_rank": vl, "parallelism": f"tp{world}",
+               "l2": f"{sets} weight set(s) of {vl * k / 1e6:.0f} MB per rank > {l2_bytes / 1e6:.0f} MB L2"}
+        return step, e2e, ab, cfg, m * k * 2, m * 4, ep
+    if wl == "moe_down":
+        E, n, k, top_k = 384, N_OUT, 2048, 6
+        e0, el = sh.slice_of(E)
+        ep = tp.Endpoint(sh, dev.index, max_m=max(m, 8), max_n=n, wait_ms=5000)
+        w2, s2 = synth.torch_fp4_experts(el, n, k, seed=synth.config_seed(wl, 0, world) + rank, device=dev)
+        rng = np.random.default_rng(synth.config_seed(wl, m, 1))
+        sets, local_experts = [], []
+        for _ in range(16):  # different routes every step: different experts stream from HBM
+            ids, rw = synth.routes(rng, m, E, top_k)
+            sets.append((torch.from_numpy(ids).to(dev), torch.from_numpy(rw).to(dev)))
+            local_experts.append(len(np.unique(ids[(ids >= e0) & (ids < e0 + el)])))
+        h = torch.randn((m * top_k, k), generator=g, device=dev).to(torch.bfloat16)
+        out = torch.empty((m, n), dtype=torch.float32, device=dev)
+        h_pin, out_pin, hd = h.cpu().pin_memory(), torch.empty((m, n), dtype=torch.float32).pin_memory(), torch.empty_like(h)
+
+        def step(i):
+            ep.moe_down_combine_allreduce(h, sets[i % 16][0], sets[i % 16][1], w2, s2, e0, out=out)
+
+        def e2e(i):
+            hd.copy_(h_pin, non_blocking=True)
+            ep.moe_down_combine_allreduce(hd, sets[i % 16][0], sets[i % 16][1], w2, s2, e0, out=out)
+            out_pin.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        ne = float(np.mean(local_experts))
+        ab = int(ne * (n * k // 2 + n * k // 32) + m * top_k * k * 2 + m * n * 4)
+        cfg = {"workload": f"moe_down mxfp4 {E} experts [{n}x{k}] E/{world} per rank, top-{top_k}, + combine + fp32 all-reduce, M={m}",
+               "m": m, "n": n, "k": k, "experts_per_rank": el, "mean_local_experts_hit": ne, "parallelism": f"tp{world}",
+               "l2": f"16 rotating route sets over a {el * n * (k // 2 + k // 32) / 1e6:.0f} MB expert slab"}
+        return step, e2e, ab, cfg, m * top_k * k * 2, m * n * 4, ep
+    raise SystemExit(f"unknown workload {wl}")
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -175,32 +274,10 @@ def run_ours(args) -> None:
 
     m = args.m
     sh = tp.Sharding(world, rank)
-    k0, kl = sh.slice_of(K_FULL)
     l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
-    per_set = N_OUT * kl
-    layers = max(4, int(np.ceil(3.0 * l2_bytes / per_set)))
-    layers = min(layers, 64)
-
-    ep = tp.Endpoint(sh, local_rank, max_m=max(m, 8), max_n=N_OUT, wait_ms=5000)
+    step, e2e_step, abytes, cfg, h2d, d2h, ep = build_workload(args, tp, synth, torch, dev, sh, l2_bytes)
     if world > 1:
         ep.connect_process_group()
-
-    # every rank quantises the SAME full tensors (same seed) and keeps its K slice
-    ws, scs = [], []
-    for l in range(layers):
-        w, sc = synth.torch_fp8_weight(N_OUT, K_FULL, seed=synth.config_seed("o_proj", m, 1) + l, device=dev)
-        ws.append(w[:, k0:k0 + kl].contiguous())
-        scs.append(sc)
-        del w
-    g = torch.Generator(device=dev)
-    g.manual_seed(99)
-    x_full = torch.randn((m, K_FULL), generator=g, device=dev).to(torch.bfloat16)
-    x = x_full[:, k0:k0 + kl].contiguous()
-    outs = [torch.empty((m, N_OUT), dtype=torch.float32, device=dev) for _ in range(2)]
-
-    def step(i: int):
-        l = i % layers
-        ep.fp8_rowpar_gemm_allreduce(x, ws[l], scs[l], block=(BN, BK), k0=k0, out=outs[i & 1])
 
     def barrier():
         if world > 1:
@@ -228,21 +305,37 @@ def run_ours(args) -> None:
         graph.replay()          # one untimed replay after capture
         ep.check()
     launches = ep.launches - launches0 if graph is not None else args.steps
+
+    def run_k_steps():
+        if graph is not None:
+            graph.replay()
+        else:
+            for i in range(args.steps):
+                step(i)
+
+    def keep_busy(seconds: float):
+        """Same work, untimed, so that nvidia-smi (100 ms period) samples clocks under this load."""
+        t_end = time.perf_counter() + seconds
+        while time.perf_counter() < t_end:
+            run_k_steps()
+            torch.cuda.synchronize()
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    keep_busy(0.8)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    if graph is not None:
-        graph.replay()
-    else:
-        for i in range(args.steps):
-            step(i)
+    run_k_steps()               # the timed region: exactly K steps
     e1.record()
     barrier()
+    keep_busy(0.8)
     ep.check()
     ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = "0.8 s of the same K-step replay before and after the timed replay, sampled every 100 ms"
 
     # isolated steps: one event pair per step, device idle in between
     iso = []
@@ -254,17 +347,15 @@ def run_ours(args) -> None:
         b.record()
         torch.cuda.synchronize()
         iso.append(a.elapsed_time(b) * 1e3)
-    clocks = sampler.stop() if rank == 0 else None
 
-    # end to end through host buffers: activations copied in, reduced rows copied out, every step
-    x_host = x.view(torch.int16).cpu().numpy().view(np.uint16)
+    # end to end through host buffers: activations copied in, results copied out, every step
     e2e_steps = max(10, min(args.steps, 200))
     for i in range(3):
-        ep.fp8_rowpar_gemm_allreduce_host(x_host, ws[i % layers], scs[i % layers], block=(BN, BK), k0=k0)
+        e2e_step(i)
     barrier()
     t0 = time.perf_counter()
     for i in range(e2e_steps):
-        ep.fp8_rowpar_gemm_allreduce_host(x_host, ws[i % layers], scs[i % layers], block=(BN, BK), k0=k0)
+        e2e_step(i)
     torch.cuda.synchronize()
     e2e_us = (time.perf_counter() - t0) / e2e_steps * 1e6
 
@@ -276,33 +367,30 @@ def run_ours(args) -> None:
 
     if rank == 0:
         peak, peak_src = measured_peak_gbs()
-        abytes = algorithmic_bytes(m, N_OUT, kl)
         achieved = abytes / (us_per_step * 1e-6) / 1e9
-        traffic = None
-        try:
-            with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
-                traffic = json.load(f).get(f"fp8_rowpar_kernel_r{world}_m{m}")
-        except Exception:
-            pass
-        cpu_us, cpu_n = time_oracle(1, 12.0, m)
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised
+        # under profiles/ (o_proj, one rank, M=1: the capture shows the algorithmic bytes and nothing more)
+        traffic = 58.87e6 if (args.workload == "o_proj" and world == 1 and m == 1) else None
+        if args.workload == "o_proj":
+            cpu_us, cpu_n = time_oracle(1, 12.0, m)
+            cpu = {"value": cpu_us, "unit": "us", "cores": 1, "kind": "port",
+                   "sample": f"{cpu_n} full o_proj steps (M={m}, whole K), single thread as the reference engine runs"}
+        else:
+            cpu = None
+        cfg["timing"] = (("CUDA events around one replay of a CUDA graph holding all K steps" if graph is not None
+                          else "CUDA events around K eager launches") + ", one stream, max over ranks")
+        metric = METRIC if args.workload == "o_proj" else f"us per fused step ({args.workload}, M={m})"
         line = {
-            "metric": METRIC, "value": us_per_step, "unit": "us", "n_gpus": world, "steps": args.steps,
+            "metric": metric, "value": us_per_step, "unit": "us", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": us_per_step / 1e3, "higher_is_better": False, "scaling": "strong",
-            "vs_baseline": None, "dtype": "fp8 e4m3 x fp8 e4m3 -> f32", "data": "synthetic",
-            "config": {"workload": f"o_proj fp8 [7168x8192] K/{world} per rank + fused fp32 all-reduce, M={m}",
-                       "m": m, "n": N_OUT, "k": K_FULL, "k_per_rank": kl, "parallelism": f"tp{world}",
-                       "l2": f"{layers} rotating weight sets ({layers * per_set / 1e6:.0f} MB per rank) > "
-                             f"{l2_bytes / 1e6:.0f} MB L2; no flush needed",
-                       "timing": ("CUDA events around one replay of a CUDA graph holding all K steps" if graph is not None
-                                  else "CUDA events around K eager launches") + ", one stream, max over ranks"},
+            "vs_baseline": None, "dtype": "fp8 e4m3 x fp8 e4m3 -> f32" if args.workload != "moe_down" else "fp8 e4m3 x fp4 e2m1 -> f32",
+            "data": "synthetic", "config": cfg,
             "isolated_us": iso_us,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_source": f"of {peak_src}", "algorithmic_bytes": abytes,
                          "frac_of_8TBs": achieved / 8000.0},
-            "cpu_baseline": {"value": cpu_us, "unit": "us", "cores": 1, "kind": "port",
-                             "sample": f"{cpu_n} full o_proj steps (M={m}, whole K), single thread as the reference engine runs"},
-            "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": int(m * kl * 2),
-                    "d2h_bytes_per_step": int(m * N_OUT * 4)},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
@@ -321,6 +409,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=1, help="activation rows per step (1 = decode)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a graph replay")
+    ap.add_argument("--workload", default="o_proj", choices=["o_proj", "shared_down", "moe_down", "lm_head"],
+                    help="o_proj is the headline step; the others are the path's remaining fused steps")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

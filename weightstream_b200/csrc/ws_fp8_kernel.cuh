@@ -291,17 +291,21 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     int redbuf = 0;
 
     const int kofs = (int)(A.k0 - kcol0 * p.bk);  // k0 modulo the scale block
-    auto mma_step = [&](uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, int kb, const float *swrow) {
+    // shared-space addresses of this lane's operands of K block 0 (advanced per block below)
+    const uint32_t q_lane = smem_u32(q_s) + (uint32_t)(g * 32 + tq * 4);
+    const uint32_t q_step = (uint32_t)(p.mp * 32);
+    const uint32_t sa_lane = smem_u32(sa_s) + (uint32_t)(tq * 8);
+    const bool has_b = g < p.mp;
+    auto mma_step = [&](uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, int kb, uint32_t swrow) {
         uint32_t b0r = 0, b1r = 0;
-        if (g < p.mp) {
-            const uint8_t *qp = q_s + ((size_t)(kb * p.mp + g) * 32 + tq * 4);
-            b0r = *reinterpret_cast<const uint32_t *>(qp);
-            b1r = *reinterpret_cast<const uint32_t *>(qp + 16);
+        if (has_b) {
+            b0r = lds_u32(q_lane + kb * q_step);
+            b1r = lds_u32(q_lane + kb * q_step + 16);
         }
         float d[4];
         mma_e4m3_16x8x32(d, a0, a1, a2, a3, b0r, b1r);
-        const float2 sa = *reinterpret_cast<const float2 *>(sa_s + kb * 8 + tq * 2);
-        const float sw = swrow[(kofs + kb * 32) >> p.bk_shift];
+        const float2 sa = lds_f32x2(sa_lane + kb * 32);
+        const float sw = lds_f32(swrow + (uint32_t)(((kofs + kb * 32) >> p.bk_shift) * 4));
         const float f0 = sa.x * sw, f1 = sa.y * sw;
         acc[0] = fmaf(d[0], f0, acc[0]);
         acc[1] = fmaf(d[1], f1, acc[1]);
@@ -313,7 +317,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         mbar_wait(full0 + s * 8, (uint32_t)(item / NS) & 1u, X.status);
         if (item == 0) WS_MARK(4);
         const uint32_t sbase = stage0 + s * kStageBytes;
-        const float *swrow = sw_s + slot * p.skb;
+        const uint32_t swrow = smem_u32(sw_s) + (uint32_t)(slot * p.skb * 4);
         for (int bi = warp; bi < nb; bi += kConsumerWarps) {
             const int box = b0 + bi;
             const uint32_t bbase = sbase + bi * pad * 128 + lm_row * 128;

@@ -289,19 +289,21 @@ __device__ __forceinline__ void moe_down_body(const MoeParams &p) {
         consumer_bar();
     };
 
+    const uint32_t q_lane = smem_u32(q_s) + (uint32_t)(g * 32 + tq * 8);
+    const uint32_t sa_lane = smem_u32(sa_s) + (uint32_t)(tq * 8);
     // One stage item: `nt` tiles of this pass, each kbox boxes wide; pair (tile j, box b) -> warps round robin.
     auto run_item = [&](int nt) {
         const int s = item % NS;
         mbar_wait(full0 + s * 8, ((uint32_t)(item / NS)) & 1u, X.status);
         const uint32_t sbase = stage0 + s * S.stage_bytes;
-        const uint8_t *scbase = smem + S.stages + (size_t)s * S.stage_bytes + S.scale_off;
+        const uint32_t scbase = sbase + S.scale_off;
         for (int pi = warp; pi < nt * kbox; pi += kConsumerWarps) {
             const int j = pi / kbox, box = pi - j * kbox;
             const uint32_t bbase = sbase + j * S.tile_bytes + box * kBoxBytes + lm_row * 128;
-            const uint8_t *sc = scbase + j * kGroupRows * kb32;
+            const uint32_t sc = scbase + j * kGroupRows * kb32 + box * 8;
             // UE8M0 bytes of the box's eight K blocks, rows g and g+8
-            const uint64_t sc0 = *reinterpret_cast<const uint64_t *>(sc + g * kb32 + box * 8);
-            const uint64_t sc1 = *reinterpret_cast<const uint64_t *>(sc + (g + 8) * kb32 + box * 8);
+            const uint2 sc0v = lds_u64(sc + g * kb32), sc1v = lds_u64(sc + (g + 8) * kb32);
+            const uint64_t sc0 = ((uint64_t)sc0v.y << 32) | sc0v.x, sc1 = ((uint64_t)sc1v.y << 32) | sc1v.x;
 #pragma unroll
             for (int kp = 0; kp < 4; ++kp) {  // two 32-wide K blocks (two 16-byte chunks) per step
                 const int kb = box * 8 + kp * 2;
@@ -315,10 +317,10 @@ __device__ __forceinline__ void moe_down_body(const MoeParams &p) {
                     uint32_t a0, a1, a2, a3;
                     fp4x8_to_e4m3(h ? w01 : w00, a0, a2);
                     fp4x8_to_e4m3(h ? w11 : w10, a1, a3);
-                    const uint2 b = *reinterpret_cast<const uint2 *>(q_s + ((size_t)(kbh * 8 + g) * 32 + tq * 8));
+                    const uint2 b = lds_u64(q_lane + kbh * 256);
                     float d[4];
                     mma_e4m3_16x8x32(d, a0, a1, a2, a3, b.x, b.y);
-                    const float2 sa = *reinterpret_cast<const float2 *>(sa_s + kbh * 8 + tq * 2);
+                    const float2 sa = lds_f32x2(sa_lane + kbh * 32);
                     const float s0 = e8m0_f32((uint32_t)(sc0 >> ((kp * 2 + h) * 8)) & 0xFFu);
                     const float s1 = e8m0_f32((uint32_t)(sc1 >> ((kp * 2 + h) * 8)) & 0xFFu);
                     float *a = acc[j & 1];
