@@ -99,7 +99,7 @@ FP8_CASES = [
 
 @pytest.mark.parametrize("n,k,scale,bn,bk,ms", FP8_CASES)
 @pytest.mark.parametrize("split", [True, False])
-@pytest.mark.parametrize("kernel", [2, 1])  # 2: tcgen05 / tensor-memory kernel, 1: mma.sync kernel
+@pytest.mark.parametrize("kernel", [0, 2, 1])  # 0: automatic (CUDA cores for 1-2 rows), 2: tcgen05 kernel, 1: mma.sync kernel
 def test_fp8_gemm_tp1(dev, tpmod, oracle, n, k, scale, bn, bk, ms, split, kernel):
     from weightstream_b200 import formats as F, synth
     rng = np.random.default_rng(synth.config_seed(f"fp8-{n}-{k}-{scale}", 0, 1))
@@ -164,7 +164,7 @@ def test_oproj_full_size_tp1(dev, tpmod, oracle):
 # ----------------------------------------------------------------------------- FP8 GEMM, TP>1
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("n,k,m", [(512, 2048, 1), (7168, 8192, 1), (7168, 8192, 5), (1024, 1024, 19)])
-@pytest.mark.parametrize("kernel", [2, 1])
+@pytest.mark.parametrize("kernel", [0, 2, 1])
 def test_fp8_gemm_allreduce_virtual_ranks(dev, tpmod, oracle, world, n, k, m, kernel):
     """K sharded over `world` ranks (engine.rs:1477-1480); partials added in rank order
     (ring.rs:399-408); every rank must hold identical bits."""
@@ -273,7 +273,7 @@ def test_wait_times_out_and_context_survives(dev, tpmod):
 # ----------------------------------------------------------------------------- lm_head
 @pytest.mark.parametrize("world", [1, 2, 8])
 @pytest.mark.parametrize("m", [1, 3])
-@pytest.mark.parametrize("kernel", [2, 1])
+@pytest.mark.parametrize("kernel", [0, 2, 1])
 def test_lm_head_small_vs_oracle(dev, tpmod, oracle, world, m, kernel):
     """Vocab-sharded head whose shards cut a 128-row scale block (as 129280/8 does): logits equal
     the oracle's, argmax equals sample.rs:13-23 on the oracle's logits."""
@@ -365,12 +365,16 @@ def moe_case(rng, m, n_experts, top_k, n, k):
     (3, 8, 2, 5120, 2304),        # reference-native expert shape
 ])
 @pytest.mark.parametrize("split", [True, False])
-def test_moe_down_combine_tp1(dev, tpmod, oracle, m, n_experts, top_k, n, k, split):
+@pytest.mark.parametrize("kernel", [0, 1])  # 0: decode form (prep kernel + CUDA-core kernel), 1: tensor-core MMA form
+def test_moe_down_combine_tp1(dev, tpmod, oracle, m, n_experts, top_k, n, k, split, kernel):
     from weightstream_b200 import formats as F
+    if kernel == 0 and not split:
+        pytest.skip("the leftover-row knob only exists in the MMA form")
     rng = np.random.default_rng(1000 + m + n + k)
     w2, s2, ids, rw, hb = moe_case(rng, m, n_experts, top_k, n, k)
     ep = tpmod.Endpoint(max_m=64, max_n=n)
     ep.set_split(split)
+    ep.set_kernel(kernel)
     try:
         out = ep.moe_down_combine_allreduce(bf16_tensor(hb, dev), torch.from_numpy(ids).to(dev),
                                             torch.from_numpy(rw).to(dev), u8(w2, dev), u8(s2, dev), 0)
@@ -384,7 +388,8 @@ def test_moe_down_combine_tp1(dev, tpmod, oracle, m, n_experts, top_k, n, k, spl
 
 @pytest.mark.parametrize("world", [2, 8])
 @pytest.mark.parametrize("m", [1, 8, 64])
-def test_moe_down_combine_virtual_ranks(dev, tpmod, oracle, world, m):
+@pytest.mark.parametrize("kernel", [0, 1])
+def test_moe_down_combine_virtual_ranks(dev, tpmod, oracle, world, m, kernel):
     """Experts sharded by id (engine.rs:1194-1195); rank partials (local ascending-id sums) added
     in rank order; identical bits on all ranks.  Some ranks own no selected expert at m=1."""
     from weightstream_b200 import formats as F
@@ -393,6 +398,7 @@ def test_moe_down_combine_virtual_ranks(dev, tpmod, oracle, world, m):
     w2, s2, ids, rw, hb = moe_case(rng, m, n_experts, top_k, n, k)
     hf = F.bf16_bits_to_f32(hb)
     grp = tpmod.LocalGroup(world, max_m=64, max_n=n)
+    grp.set_kernel(kernel)
     try:
         hd, idd, rwd = bf16_tensor(hb, dev), torch.from_numpy(ids).to(dev), torch.from_numpy(rw).to(dev)
         w2d, s2d = u8(w2, dev), u8(s2, dev)

@@ -17,6 +17,7 @@
 #include "ws_fp8_umma_kernel.cuh"
 #include "ws_misc_kernels.cuh"
 #include "ws_moe_kernel.cuh"
+#include "ws_moe_gemv_kernel.cuh"
 
 using namespace ws;
 
@@ -36,13 +37,18 @@ struct ws_tp {
     uint64_t timeout_ns = 0;
     int split = 1;
     int pdl = 1;         // programmatic dependent launch for the FP8 mma.sync kernel
-    int kernel_sel = 0;  // 0: automatic (mma.sync kernel for decode), 1: mma.sync kernel, 2: tcgen05 kernel when the shape fits
+    int kernel_sel = 0;  // 0: automatic (CUDA cores for 1-2 rows, mma.sync for 3-8), 1: mma.sync, 2: tcgen05 when the shape fits
     // host-buffer entry points
     cudaStream_t hstream = nullptr;
     void *pin = nullptr;
     size_t pin_bytes = 0;
     void *dev_stage = nullptr;
     size_t dev_stage_bytes = 0;
+    // MoE decode step: routes quantised once per step, pass table, large-m accumulators
+    uint8_t *moe_work = nullptr;
+    size_t moe_work_bytes = 0;
+    float *moe_acc = nullptr;
+    size_t moe_acc_bytes = 0;
     std::string err;
 };
 
@@ -131,14 +137,14 @@ ws_status_t set_smem(ws_tp *tp, K kernel) {
 
 template <typename P>
 ws_status_t launch(ws_tp *tp, void (*kernel)(P), const P &params, int ncta, int nvr, int threads, size_t smem,
-                   cudaStream_t stream, bool pdl = false) {
+                   cudaStream_t stream, bool pdl = false, bool waits_on_peers = true) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)ncta, (unsigned)nvr, 1);
     cfg.blockDim = dim3((unsigned)threads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
-    if (nvr > 1) {
+    if (nvr > 1 && waits_on_peers) {
         // Virtual ranks sharing one device wait on one another inside the kernel: they must be
         // co-resident, which a cooperative launch guarantees (or refuses).
         attr[0].id = cudaLaunchAttributeCooperative;
@@ -228,7 +234,8 @@ ws_status_t ws_tp_create(int32_t world, int32_t rank, int32_t device, const ws_t
     if (cudaDeviceSynchronize() != cudaSuccess) return bail(WS_ERR_CUDA);
     tp->peers[rank] = tp->sym;
     if (world == 1) tp->connected = true;
-    if (set_smem(tp, fp8_rowpar_kernel) != WS_OK || set_smem(tp, moe_down_kernel) != WS_OK ||
+    if (set_smem(tp, moe_gemv_kernel) != WS_OK || set_smem(tp, fp8_rowpar_kernel<0>) != WS_OK || set_smem(tp, fp8_rowpar_kernel<1>) != WS_OK ||
+        set_smem(tp, fp8_rowpar_kernel<2>) != WS_OK || set_smem(tp, moe_down_kernel) != WS_OK ||
         set_smem(tp, fp8_umma_kernel) != WS_OK)
         return bail(WS_ERR_CUDA);
     *out = tp;
@@ -243,6 +250,8 @@ ws_status_t ws_tp_destroy(ws_tp_t *tp) {
     if (tp->hstream) cudaStreamDestroy(tp->hstream);
     if (tp->pin) cudaFreeHost(tp->pin);
     if (tp->dev_stage) cudaFree(tp->dev_stage);
+    if (tp->moe_work) cudaFree(tp->moe_work);
+    if (tp->moe_acc) cudaFree(tp->moe_acc);
     if (tp->sym) cudaFree(tp->sym);
     if (tp->contrib) cudaFree(tp->contrib);
     if (tp->counters) cudaFree(tp->counters);
@@ -478,12 +487,15 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
     p.gran = ragged_granularity(p.n, ncta);
     p.nslot_max = (Gm * kGroupRows) / p.bn + 2 + 2;
     p.part_rows = (Gm + 2) * kGroupRows;  // whole tiles + at most two ragged tiles
-    const Fp8Smem fixed = fp8_smem_layout(0, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows);
+    // One or two activation rows: CUDA-core dot products; more: the tensor-core MMA.
+    const int gt = (t0->kernel_sel != 1 && mt <= 2) ? mt : 0;
+    void (*const kernel)(Fp8Params) = gt == 1 ? fp8_rowpar_kernel<1> : gt == 2 ? fp8_rowpar_kernel<2> : fp8_rowpar_kernel<0>;
+    const Fp8Smem fixed = fp8_smem_layout(0, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows, gt);
     int ns = (kSmemBudget - fixed.total) / kStageBytes;
     if (ns > kMaxStages) ns = kMaxStages;
     if (ns < 2) return fail(t0, WS_ERR_CAPACITY, "shapes m=%d n=%d k=%d leave no room for the weight stage ring", p.m, p.n, p.k);
     p.nstages = ns;
-    const size_t smem = (size_t)fp8_smem_layout(ns, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows).total + 1024;
+    const size_t smem = (size_t)fp8_smem_layout(ns, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows, gt).total + 1024;
 
     for (int i = 0; i < n; ++i) {
         ws_tp *t = ranks[i];
@@ -508,7 +520,7 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
     for (int i = 0; i < n; ++i) ranks[i]->step++;
     if (same_device) {
         WS_CUDA(t0, cudaSetDevice(t0->device));
-        return launch(t0, fp8_rowpar_kernel, p, ncta, n, kThreads, smem, static_cast<cudaStream_t>(streams ? streams[0] : nullptr), t0->pdl != 0);
+        return launch(t0, kernel, p, ncta, n, fp8_threads(gt), smem, static_cast<cudaStream_t>(streams ? streams[0] : nullptr), t0->pdl != 0);
     }
     for (int i = 0; i < n; ++i) {  // one launch per device, each sees itself as virtual rank 0
         Fp8Params q = p;
@@ -516,7 +528,7 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
         q.tmap[0][0] = p.tmap[i][0];
         q.tmap[0][1] = p.tmap[i][1];
         WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
-        ws_status_t s = launch(ranks[i], fp8_rowpar_kernel, q, ncta, 1, kThreads, smem,
+        ws_status_t s = launch(ranks[i], kernel, q, ncta, 1, fp8_threads(gt), smem,
                                static_cast<cudaStream_t>(streams ? streams[i] : nullptr), t0->pdl != 0);
         if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
     }
@@ -592,7 +604,115 @@ ws_status_t ws_lm_head_allgather_argmax(ws_tp_t *tp, const ws_lm_head_args_t *ar
     return ws_lm_head_allgather_argmax_group(r, 1, args, s);
 }
 
+
 // ------------------------------------------------------------------------------ MoE down
+static ws_status_t ensure_moe_scratch(ws_tp *tp, size_t work_bytes, size_t acc_bytes) {
+    WS_CUDA(tp, cudaSetDevice(tp->device));
+    if (work_bytes > tp->moe_work_bytes) {
+        if (tp->moe_work) cudaFree(tp->moe_work);
+        tp->moe_work = nullptr;
+        tp->moe_work_bytes = 0;
+        WS_CUDA(tp, cudaMalloc(&tp->moe_work, work_bytes));
+        tp->moe_work_bytes = work_bytes;
+    }
+    if (acc_bytes > tp->moe_acc_bytes) {
+        if (tp->moe_acc) cudaFree(tp->moe_acc);
+        tp->moe_acc = nullptr;
+        tp->moe_acc_bytes = 0;
+        WS_CUDA(tp, cudaMalloc(&tp->moe_acc, acc_bytes));
+        tp->moe_acc_bytes = acc_bytes;
+    }
+    return WS_OK;
+}
+
+// Decode form of the MoE step: the prep kernel (activation quantisation once per route, pass
+// table) followed by the persistent matrix-vector kernel.  Arguments are already validated.
+static ws_status_t moe_gemv_step(ws_tp *const *ranks, int n, const ws_moe_down_args_t *args, void *const *streams,
+                                 int ncta, bool same) {
+    ws_tp *t0 = ranks[0];
+    const ws_moe_down_args_t &a0 = args[0];
+    MoeGemvParams p{};
+    p.m = a0.m; p.n = a0.n; p.k = a0.k; p.top_k = a0.top_k; p.world = t0->world;
+    p.timeout_ns = t0->timeout_ns;
+    p.lay = t0->lay;
+    const int kbytes = p.k / 2, kbox = kbytes / 128, kb32 = p.k / 32;
+    const int nslice = moe_gemv_slices(p.k);
+    // rows are dealt out in units whose scale bytes are a multiple of 16 (they travel by bulk copy)
+    p.gran = 1;
+    while ((p.gran * kb32) % 16) p.gran *= 2;
+    int rows_max = 0;
+    for (int c = 0; c < ncta; ++c) {
+        int a, b;
+        moe_gemv_rows(p.n, p.gran, ncta, c, a, b);
+        rows_max = std::max(rows_max, b - a);
+    }
+    if (rows_max < 1) rows_max = p.gran;
+    p.acc_rows = rows_max;
+    p.acc_global = (size_t)nslice * p.m * rows_max * 4 > 16384 ? 1 : 0;
+    auto stage_bytes = [&](int pr) { return (int)align_up((int64_t)kbox * ((pr + 7) / 8 * 8) * 128 + (int64_t)pr * kb32, 1024); };
+    const int fixed = moe_gemv_smem(0, 0, p.k, p.m, p.acc_rows, p.acc_global).total;
+    // one stage holds a CTA's whole row range of one expert when three of them fit; otherwise
+    // the range is walked in panels of a multiple of 16 rows
+    p.panel_rows = rows_max;
+    if (3 * stage_bytes(p.panel_rows) > kSmemBudget - fixed) {
+        p.panel_rows = (rows_max + 15) / 16 * 16;
+        while (p.panel_rows > 16 && 3 * stage_bytes(p.panel_rows) > kSmemBudget - fixed) p.panel_rows -= 16;
+    }
+    p.stage_bytes = stage_bytes(p.panel_rows);
+    p.rows_pitch = (p.panel_rows + 7) / 8 * 8;
+    p.scale_off = kbox * p.rows_pitch * 128;
+    int ns = (kSmemBudget - fixed) / p.stage_bytes;
+    if (ns > kMaxStages) ns = kMaxStages;
+    if (ns < 2) return fail(t0, WS_ERR_CAPACITY, "shapes m=%d n=%d k=%d leave no room for the weight stage ring", p.m, p.n, p.k);
+    p.nstages = ns;
+    const size_t smem = (size_t)moe_gemv_smem(ns, p.stage_bytes, p.k, p.m, p.acc_rows, p.acc_global).total + 1024;
+
+    MoePrepParams q{};
+    q.m = p.m; q.k = p.k; q.top_k = p.top_k; q.h_dtype = a0.h_dtype;
+    const size_t work_bytes = (size_t)moe_work_layout(p.k).total;
+    const size_t acc_bytes = p.acc_global ? (size_t)nslice * p.m * p.n * 4 : 0;
+    for (int i = 0; i < n; ++i) {
+        const ws_moe_down_args_t &a = args[i];
+        ws_status_t s = ensure_moe_scratch(ranks[i], work_bytes, acc_bytes);
+        if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
+        for (int b = 0; b < 2; ++b) {
+            s = make_tmap(ranks[i], &p.tmap[i][b], a.w2, (uint64_t)a.e_len * a.n, (uint64_t)kbytes, (uint64_t)kbytes,
+                          b ? (uint32_t)p.gran : (uint32_t)kGroupRows);
+            if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
+        }
+        MoeGemvRank &r = p.r[i];
+        r.s2 = a.s2; r.work = ranks[i]->moe_work; r.out = a.out; r.acc_g = ranks[i]->moe_acc;
+        r.e_start = a.e_start; r.e_len = a.e_len;
+        r.ctx = make_ctx(ranks[i]);
+        MoePrepRank &pr = q.r[i];
+        pr.h = a.h; pr.route_ids = a.route_ids; pr.route_w = a.route_w; pr.work = ranks[i]->moe_work;
+        pr.ldh = a.ldh; pr.e_start = a.e_start; pr.e_len = a.e_len;
+    }
+    for (int i = 0; i < n; ++i) ranks[i]->step++;
+    const int nblk = p.m * p.top_k + 1;
+    if (same) {
+        WS_CUDA(t0, cudaSetDevice(t0->device));
+        cudaStream_t cs = static_cast<cudaStream_t>(streams ? streams[0] : nullptr);
+        ws_status_t s = launch(t0, moe_prep_kernel, q, nblk, n, 256, 0, cs, t0->pdl != 0, false);
+        if (s != WS_OK) return s;
+        return launch(t0, moe_gemv_kernel, p, ncta, n, kMoeGemvThreads, smem, cs, t0->pdl != 0);
+    }
+    for (int i = 0; i < n; ++i) {
+        MoeGemvParams pi = p;
+        pi.r[0] = p.r[i];
+        pi.tmap[0][0] = p.tmap[i][0];
+        pi.tmap[0][1] = p.tmap[i][1];
+        MoePrepParams qi = q;
+        qi.r[0] = q.r[i];
+        WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
+        cudaStream_t cs = static_cast<cudaStream_t>(streams ? streams[i] : nullptr);
+        ws_status_t s = launch(ranks[i], moe_prep_kernel, qi, nblk, 1, 256, 0, cs, t0->pdl != 0, false);
+        if (s == WS_OK) s = launch(ranks[i], moe_gemv_kernel, pi, ncta, 1, kMoeGemvThreads, smem, cs, t0->pdl != 0);
+        if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
+    }
+    return WS_OK;
+}
+
 ws_status_t ws_moe_down_combine_allreduce_group(ws_tp_t *const *ranks, int32_t n, const ws_moe_down_args_t *args,
                                                 void *const *streams) {
     int ncta;
@@ -619,6 +739,12 @@ ws_status_t ws_moe_down_combine_allreduce_group(ws_tp_t *const *ranks, int32_t n
     }
     if (a0.m > t0->cfg.max_m || a0.n > t0->cfg.max_n)
         return fail(t0, WS_ERR_CAPACITY, "m=%d n=%d exceed the endpoint's max_m=%d max_n=%d", a0.m, a0.n, t0->cfg.max_m, t0->cfg.max_n);
+
+    int e_len_all = args[0].e_len;
+    for (int i = 0; i < n; ++i)
+        if (args[i].e_len != e_len_all) return fail(t0, WS_ERR_INVALID, "ranks must hold equally many experts");
+    if (t0->kernel_sel != 1 && a0.k <= 32 * 32 * kMoeGemvWarps)  // decode form: CUDA-core matrix-vector products
+        return moe_gemv_step(ranks, n, args, streams, ncta, same);
 
     MoeParams p{};
     p.m = a0.m; p.n = a0.n; p.k = a0.k; p.top_k = a0.top_k; p.h_dtype = a0.h_dtype; p.world = t0->world;
@@ -884,7 +1010,7 @@ ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *a, int32_t devi
             }
             int sms = 0;
             ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-            if (ce == cudaSuccess) ce = cudaFuncSetAttribute(fp8_rowpar_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (ce == cudaSuccess) ce = cudaFuncSetAttribute(fp8_rowpar_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
             if (ce != cudaSuccess) { set_err(err, err_len, "device set-up: %s", cudaGetErrorString(ce)); return WS_ERR_CUDA; }
             g_static_sm_count[device] = sms;
             g_static_scratch_addr[device] = static_cast<unsigned char *>(ptr);
@@ -912,11 +1038,11 @@ ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *a, int32_t devi
     p.ragged = Gm < 8 ? 1 : 0;
     p.gran = ragged_granularity(p.n, ncta);
     p.part_rows = (Gm + 2) * kGroupRows;
-    const Fp8Smem fixed = fp8_smem_layout(0, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows);
+    const Fp8Smem fixed = fp8_smem_layout(0, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows, 0);
     int ns = std::min((kSmemBudget - fixed.total) / kStageBytes, (int)kMaxStages);
     if (ns < 2) { set_err(err, err_len, "shapes m=%d n=%d k=%d leave no room for the weight stage ring", p.m, p.n, p.k); return WS_ERR_CAPACITY; }
     p.nstages = ns;
-    const size_t smem = (size_t)fp8_smem_layout(ns, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows).total + 1024;
+    const size_t smem = (size_t)fp8_smem_layout(ns, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows, 0).total + 1024;
     Fp8RankArgs &r = p.r[0];
     for (int b = 0; b < 2; ++b) {
         st = make_tmap(&probe_err, &p.tmap[0][b], a->w, (uint64_t)a->n, (uint64_t)a->k, (uint64_t)a->ldw,
@@ -930,7 +1056,7 @@ ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *a, int32_t devi
     r.ctx.status = r.ctx.counters + kMaxShared;
     r.ctx.step_ctr = r.ctx.counters + kMaxShared + 2;
     r.ctx.rank = 0;
-    fp8_rowpar_kernel<<<dim3((unsigned)ncta, 1, 1), kThreads, smem, cs>>>(p);
+    fp8_rowpar_kernel<0><<<dim3((unsigned)ncta, 1, 1), kThreads, smem, cs>>>(p);
     ce = cudaGetLastError();
     if (ce != cudaSuccess) { set_err(err, err_len, "kernel launch: %s", cudaGetErrorString(ce)); return WS_ERR_CUDA; }
     return WS_OK;

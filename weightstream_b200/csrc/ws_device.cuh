@@ -15,9 +15,12 @@ constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;  // + one TMA producer warp
 constexpr int kBoxBytes = 2048;                  // one TMA box: 16 rows x 128 bytes
-constexpr int kBoxesPerStage = 16;
+#ifndef WS_BOXES_PER_STAGE
+#define WS_BOXES_PER_STAGE 16
+#endif
+constexpr int kBoxesPerStage = WS_BOXES_PER_STAGE;
 constexpr int kStageBytes = kBoxBytes * kBoxesPerStage;  // 32 KB
-constexpr int kMaxStages = 12;
+constexpr int kMaxStages = 16;
 constexpr int kMaxCtas = 160;    // persistent CTAs per rank (one per SM on B200: 148)
 constexpr int kMaxShared = 160;  // output row groups whose K range is split across CTAs
 constexpr int kMaxRuns = 16;     // split contributions one CTA may produce
@@ -179,6 +182,62 @@ __device__ __forceinline__ float2 lds_f32x2(uint32_t a) {
     return v;
 }
 
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_u128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+
+// ---- CUDA-core dot products (decode rows with one or two tokens)
+// Two E4M3 bytes (the low 16 bits of v) -> f16x2, exact.
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t v) {
+    uint32_t r;
+    asm("{.reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t;}" : "=r"(r) : "r"(v));
+    return r;
+}
+// Two E2M1 codes (the low byte of v; low nibble -> low half) -> f16x2, exact.
+__device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t v) {
+    uint32_t r;
+    asm("{.reg .b8 b; .reg .b16 t; cvt.u16.u32 t, %1; cvt.u8.u16 b, t; cvt.rn.f16x2.e2m1x2 %0, b;}" : "=r"(r) : "r"(v));
+    return r;
+}
+// f16x2 -> two f32 (exact).
+__device__ __forceinline__ float2 f16x2_to_f32x2(uint32_t v) {
+    float2 r;
+    asm("{.reg .f16 l, h; mov.b32 {l, h}, %2; cvt.f32.f16 %0, l; cvt.f32.f16 %1, h;}" : "=f"(r.x), "=f"(r.y) : "r"(v));
+    return r;
+}
+// Two E4M3 bytes -> two f32: the low (H = 0) or high (H = 1) half of v.
+template <int H>
+__device__ __forceinline__ float2 e4m3x2_to_f32x2(uint32_t v) {
+    uint32_t h;
+    if (H == 0) asm("{.reg .b16 l, h; mov.b32 {l, h}, %1; cvt.rn.f16x2.e4m3x2 %0, l;}" : "=r"(h) : "r"(v));
+    else        asm("{.reg .b16 l, h; mov.b32 {l, h}, %1; cvt.rn.f16x2.e4m3x2 %0, h;}" : "=r"(h) : "r"(v));
+    return f16x2_to_f32x2(h);
+}
+// (s.x, s.y) += (a.x * b.x, a.y * b.y): one packed fp32 FMA (two lanes' worth of work per issue slot).
+__device__ __forceinline__ void fma_f32x2(float2 &s, float2 a, float2 b) {
+    asm("{.reg .b64 ra, rb, rc; mov.b64 ra, {%2, %3}; mov.b64 rb, {%4, %5}; mov.b64 rc, {%0, %1};"
+        " fma.rn.f32x2 rc, ra, rb, rc; mov.b64 {%0, %1}, rc;}"
+        : "+f"(s.x), "+f"(s.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+}
+// s += a.lo * b.lo + a.hi * b.hi with f16 operands and fp32 accumulation: the products of two
+// 4-significant-bit values are exact, every add rounds once in fp32.
+__device__ __forceinline__ void fma2_f16(float &s, uint32_t a, uint32_t b) {
+    asm("{.reg .f16 a0, a1, b0, b1; mov.b32 {a0, a1}, %1; mov.b32 {b0, b1}, %2;"
+        " fma.rn.f32.f16 %0, a0, b0, %0; fma.rn.f32.f16 %0, a1, b1, %0;}"
+        : "+f"(s) : "r"(a), "r"(b));
+}
+
+template <int N>
+__device__ __forceinline__ void consumer_bar_n() {  // the N consumer threads only
+    asm volatile("bar.sync 1, %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ void consumer_bar() {  // the consumer warps only
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
 }

@@ -5,9 +5,16 @@
 // rows that are left over, so all SMs stream the same number of bytes and nothing is combined
 // across CTAs.  Weight tiles arrive by TMA into a ring of 32 KB stages filled by one producer
 // warp: 16-row x 128-byte boxes for whole tiles, 8/4/2/1-row boxes for the ragged rows, all
-// 128B-swizzled.  Eight consumer warps feed them to the FP8 tensor-core MMA against
-// activations that the prologue quantised exactly as the reference does, and apply the
-// activation- and weight-block scales per 32-wide K block in fp32.
+// 128B-swizzled.  The prologue quantises the activations exactly as the reference does; eight
+// consumer warps then multiply the staged rows with them and apply the activation- and
+// weight-block scales per 32-wide K block in fp32.  Two formulations of that product:
+//   GT = 1, 2 (one or two activation rows): CUDA cores.  A lane owns 16 bytes of a row
+//     (128-bit shared load), converts them to f16 pairs and accumulates exact products in fp32
+//     (fma.rn.f32.f16); the eight lanes of a row are combined by shuffles at the end of a tile.
+//     About 1.5 lane-instructions per weight byte, so HBM, not issue, bounds it.
+//   GT = 0 (three to eight rows): the FP8 tensor-core MMA m16n8k32, one per 32-wide K block.
+//     Its issue rate caps streaming near 70 % of HBM bandwidth, which is why it is not used
+//     for the narrow cases.
 //
 // Exchange (world > 1): a CTA stores its rows' fp32 partials into slot [my rank] of every
 // peer's exchange memory and then releases one flag per peer; it waits for the same CTA of
@@ -63,19 +70,29 @@ struct alignas(64) Fp8Params {
     Fp8RankArgs r[WS_MAX_WORLD];
 };
 
+// Consumer warps per CTA: the tensor-core formulation is bound by the MMA issue rate and gains
+// nothing from more warps; the CUDA-core one needs the extra warps to cover load and FMA latency.
+#ifndef WS_GEMV_WARPS
+#define WS_GEMV_WARPS 16
+#endif
+__host__ __device__ constexpr int fp8_consumer_warps(int gt) { return gt > 0 ? WS_GEMV_WARPS : kConsumerWarps; }
+__host__ __device__ constexpr int fp8_threads(int gt) { return (fp8_consumer_warps(gt) + 1) * 32; }  // + the TMA producer warp
+
 struct Fp8Smem {  // byte offsets from the 1024-aligned base
     int32_t stages, q, sa, sw, red, part, bars, misc, total;
 };
 
+// gt: 0 for the MMA formulation (activations kept as E4M3 bytes, [kb][tok][32]), else the number
+// of activation rows of the CUDA-core formulation (kept as f16, [tok][kbox*128]).
 __host__ __device__ inline Fp8Smem fp8_smem_layout(int nstages, int kbox, int mp, int nslot_max, int skb,
-                                                   int m, int part_rows) {
+                                                   int m, int part_rows, int gt) {
     Fp8Smem s{};
     int o = 0;
     s.stages = o; o += nstages * kStageBytes;
-    s.q = o;      o += kbox * 4 * mp * 32;
+    s.q = o;      o += gt > 0 ? kbox * 128 * 2 * gt : kbox * 4 * mp * 32;
     s.sa = o;     o += kbox * 4 * 8 * 4;
     s.sw = o;     o += ((nslot_max * skb * 4 + 15) / 16) * 16;
-    s.red = o;    o += 2 * kConsumerWarps * 128 * 4;
+    s.red = o;    o += 2 * fp8_consumer_warps(gt) * 128 * 4;
     s.part = o;   o += ((m * part_rows * 4 + 15) / 16) * 16;
     s.bars = o;   o += 2 * kMaxStages * 8;
     s.misc = o;   o += 128;
@@ -120,11 +137,13 @@ __device__ __forceinline__ bool cand_better(float v, uint32_t i, float bv, uint3
     return v > bv || (v == bv && i < bi);
 }
 
+template <int GT>
 __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     uint8_t *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
 
+    constexpr int CW = fp8_consumer_warps(GT), CT = CW * 32;  // consumer warps / threads of this formulation
     const int vr = blockIdx.y, cta = blockIdx.x, ncta = gridDim.x;
     const Fp8RankArgs &A = p.r[vr];
     const RankCtx &X = A.ctx;
@@ -145,7 +164,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     // stage always carries 16-32 KB: one box column = tpad rows x 128 bytes.
     auto tpad = [](int cnt) { return cnt > 8 ? 16 : cnt > 4 ? 8 : cnt > 2 ? 4 : cnt > 1 ? 2 : 1; };
 
-    const Fp8Smem S = fp8_smem_layout(p.nstages, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows);
+    const Fp8Smem S = fp8_smem_layout(p.nstages, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows, GT);
     uint8_t *q_s = smem + S.q;
     float *sa_s = reinterpret_cast<float *>(smem + S.sa);
     float *sw_s = reinterpret_cast<float *>(smem + S.sw);
@@ -159,7 +178,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(full0 + s * 8, 1);
-            mbar_init(empty0 + s * 8, kConsumerWarps);
+            mbar_init(empty0 + s * 8, CW);
         }
         mbar_fence_init();
     }
@@ -169,7 +188,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     // Let the next kernel on the stream begin (it only prefetches weights until its own wait).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    if (warp == kConsumerWarps) {
+    if (warp == CW) {
         // ------------------------------------------------------------ TMA producer warp
         int item = 0;
         for (int t = 0; t < ntile; ++t) {
@@ -233,23 +252,23 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         float pre[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const int i = tid + u * kConsumerThreads;
+            const int i = tid + u * CT;
             pre[u] = i < nsw ? load_scale(i) : 0.0f;
         }
         if (tid == 0) WS_MARK2(2);
-        for (int i = tid; i < kbox * 4 * 8; i += kConsumerThreads)  // tokens the launch does not carry
+        for (int i = tid; i < kbox * 4 * 8; i += CT)  // tokens the launch does not carry
             if ((i & 7) >= p.mp) sa_s[i] = 0.0f;
         if (tid == 0) WS_MARK2(3);
         const int chunks_per_row = kbox * 16;  // 8-element chunks over the padded K
         const int total = p.mp * chunks_per_row;
         // four chunks per thread and pass: all loads are in flight before the first is used
-        for (int c0 = tid; c0 < ((total + 31) & ~31); c0 += 4 * kConsumerThreads) {
+        for (int c0 = tid; c0 < ((total + 31) & ~31); c0 += 4 * CT) {
             float v[4][8];
             int tok[4], ch[4];
             bool valid[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const int c = c0 + u * kConsumerThreads;
+                const int c = c0 + u * CT;
                 tok[u] = c / chunks_per_row;
                 ch[u] = c - tok[u] * chunks_per_row;
                 valid[u] = (c < total) && (tok[u] < p.m) && (ch[u] * 8 < p.k);
@@ -257,15 +276,23 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const int c = c0 + u * kConsumerThreads;
+                const int c = c0 + u * CT;
                 if (c >= ((total + 31) & ~31)) break;  // warp-uniform
                 int e;
                 uint32_t lo, hi;
                 act_quant8(v[u], e, lo, hi);
                 if (c < total) {
                     const int kb = ch[u] >> 2;
-                    *reinterpret_cast<uint2 *>(q_s + ((size_t)(kb * p.mp + tok[u]) * 32 + (ch[u] & 3) * 8)) =
-                        valid[u] ? make_uint2(lo, hi) : make_uint2(0u, 0u);
+                    if constexpr (GT > 0) {  // f16 copies of the quantised values (exact)
+                        uint4 hv = make_uint4(0u, 0u, 0u, 0u);
+                        if (valid[u])
+                            hv = make_uint4(e4m3x2_to_f16x2(lo), e4m3x2_to_f16x2(lo >> 16), e4m3x2_to_f16x2(hi),
+                                            e4m3x2_to_f16x2(hi >> 16));
+                        *reinterpret_cast<uint4 *>(q_s + ((size_t)tok[u] * chunks_per_row + ch[u]) * 16) = hv;
+                    } else {
+                        *reinterpret_cast<uint2 *>(q_s + ((size_t)(kb * p.mp + tok[u]) * 32 + (ch[u] & 3) * 8)) =
+                            valid[u] ? make_uint2(lo, hi) : make_uint2(0u, 0u);
+                    }
                     if ((ch[u] & 3) == 0) sa_s[kb * 8 + tok[u]] = valid[u] ? pow2_f32(e) : 0.0f;
                 }
             }
@@ -273,13 +300,13 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         if (tid == 0) WS_MARK2(4);
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const int i = tid + u * kConsumerThreads;
+            const int i = tid + u * CT;
             if (i < nsw) sw_s[sw_index(i)] = pre[u];
         }
-        for (int i = tid + 4 * kConsumerThreads; i < nsw; i += kConsumerThreads) sw_s[sw_index(i)] = load_scale(i);
+        for (int i = tid + 4 * CT; i < nsw; i += CT) sw_s[sw_index(i)] = load_scale(i);
     }
     if (tid == 0) WS_MARK2(5);
-    consumer_bar();
+    consumer_bar_n<CT>();
     if (tid == 0) WS_MARK2(6);
     WS_MARK(1);
 
@@ -318,7 +345,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         if (item == 0) WS_MARK(4);
         const uint32_t sbase = stage0 + s * kStageBytes;
         const uint32_t swrow = smem_u32(sw_s) + (uint32_t)(slot * p.skb * 4);
-        for (int bi = warp; bi < nb; bi += kConsumerWarps) {
+        for (int bi = warp; bi < nb; bi += CW) {
             const int box = b0 + bi;
             const uint32_t bbase = sbase + bi * pad * 128 + lm_row * 128;
             const uint32_t sw7 = (uint32_t)((bi * pad + lm_row) & 7);  // 128B-swizzle phase of this row's address
@@ -344,18 +371,118 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     // Sum the consumer warps' accumulators in warp order; thread t < 128 ends with
     // the value of (row = t & 15, tok = t >> 4).
     auto reduce_warps = [&]() -> float {
-        float *rb = red_s + (redbuf * kConsumerWarps + warp) * 128;
+        float *rb = red_s + (redbuf * CW + warp) * 128;
         rb[(2 * tq) * 16 + g] = acc[0];
         rb[(2 * tq + 1) * 16 + g] = acc[1];
         rb[(2 * tq) * 16 + g + 8] = acc[2];
         rb[(2 * tq + 1) * 16 + g + 8] = acc[3];
-        consumer_bar();
+        consumer_bar_n<CT>();
         float v = 0.0f;
         if (tid < 128) {
-            const float *r0 = red_s + redbuf * kConsumerWarps * 128 + tid;
+            const float *r0 = red_s + redbuf * CW * 128 + tid;
             v = r0[0];
 #pragma unroll
-            for (int w = 1; w < kConsumerWarps; ++w) v += r0[w * 128];
+            for (int w = 1; w < CW; ++w) v += r0[w * 128];
+        }
+        redbuf ^= 1;
+        return v;
+    };
+
+    // ---- CUDA-core formulation.  Lane = (row 4j + rsub of the tile, 16-byte chunk cch of the box);
+    // acc2[tok][j] collects this lane's share of row 4j + rsub (even / odd elements) over every box
+    // its warp visits.  The block scale (activation x weight) is folded into the activation operand
+    // once per box, so the inner loop is conversions and packed FMAs only.
+    constexpr int GTn = GT > 0 ? GT : 1;
+    float2 acc2[GTn][4];
+    const int rsub = lane >> 3, cch = lane & 7;
+    // whole tiles: row 4j + rsub sits at j * 512 + its swizzled chunk; the swizzle phase (row & 7)
+    // only depends on the parity of j
+    const uint32_t off_e = (uint32_t)(rsub * 128 + ((cch ^ rsub) << 4));
+    const uint32_t off_o = (uint32_t)((rsub + 4) * 128 + ((cch ^ rsub ^ 4) << 4));
+    auto dot16 = [&](const uint4 w, const float2 (&xf)[GTn][8], int j) {
+        const float2 w0 = e4m3x2_to_f32x2<0>(w.x), w1 = e4m3x2_to_f32x2<1>(w.x);
+        const float2 w2 = e4m3x2_to_f32x2<0>(w.y), w3 = e4m3x2_to_f32x2<1>(w.y);
+        const float2 w4 = e4m3x2_to_f32x2<0>(w.z), w5 = e4m3x2_to_f32x2<1>(w.z);
+        const float2 w6 = e4m3x2_to_f32x2<0>(w.w), w7 = e4m3x2_to_f32x2<1>(w.w);
+#pragma unroll
+        for (int tk = 0; tk < GTn; ++tk) {
+            float2 a = acc2[tk][j];
+            fma_f32x2(a, w0, xf[tk][0]); fma_f32x2(a, w1, xf[tk][1]);
+            fma_f32x2(a, w2, xf[tk][2]); fma_f32x2(a, w3, xf[tk][3]);
+            fma_f32x2(a, w4, xf[tk][4]); fma_f32x2(a, w5, xf[tk][5]);
+            fma_f32x2(a, w6, xf[tk][6]); fma_f32x2(a, w7, xf[tk][7]);
+            acc2[tk][j] = a;
+        }
+    };
+    auto run_item_gemv = [&](int b0, int nb, int slot, int pad) {
+        const int s = item % NS;
+        mbar_wait(full0 + s * 8, (uint32_t)(item / NS) & 1u, X.status);
+        if (item == 0) WS_MARK(4);
+        const uint32_t sbase = stage0 + s * kStageBytes;
+        const uint32_t swrow = smem_u32(sw_s) + (uint32_t)(slot * p.skb * 4);
+        const uint32_t xbase = smem_u32(q_s) + (uint32_t)(cch * 32);
+#ifndef WS_PROBE_NOCOMPUTE
+        for (int bi = warp; bi < nb; bi += CW) {
+            const int box = b0 + bi;
+            const int kb = box * 4 + (cch >> 1);  // the 32-wide K block of this lane's chunk
+            const float sw = kb < kb32 ? lds_f32(swrow + (uint32_t)(((kofs + kb * 32) >> p.bk_shift) * 4)) : 0.0f;
+            float2 xf[GTn][8];
+#pragma unroll
+            for (int tk = 0; tk < GTn; ++tk) {
+                const uint32_t xa = xbase + (uint32_t)((tk * kbox + box) * 256);
+                const uint4 x0 = lds_u128(xa), x1 = lds_u128(xa + 16);
+                const float f = kb < kb32 ? lds_f32(smem_u32(sa_s) + (uint32_t)((kb * 8 + tk) * 4)) * sw : 0.0f;
+                const uint32_t xh[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float2 v = f16x2_to_f32x2(xh[i]);
+                    xf[tk][i] = make_float2(v.x * f, v.y * f);
+                }
+            }
+            const uint32_t bbase = sbase + bi * pad * 128;
+            if (pad == kGroupRows) {  // whole tile: four rows per lane, straight-line
+                const uint4 wa = lds_u128(bbase + off_e), wb = lds_u128(bbase + off_o);
+                const uint4 wc = lds_u128(bbase + 1024 + off_e), wd = lds_u128(bbase + 1024 + off_o);
+                dot16(wa, xf, 0);
+                dot16(wb, xf, 1);
+                dot16(wc, xf, 2);
+                dot16(wd, xf, 3);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (4 * j < pad) {  // warp-uniform: rows the stage holds
+                        const int r = 4 * j + rsub;
+                        dot16(lds_u128(bbase + r * 128 + ((uint32_t)(cch ^ ((bi * pad + r) & 7)) << 4)), xf, j);
+                    }
+                }
+            }
+        }
+#endif
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + s * 8);
+        ++item;
+    };
+    // Combine the eight lanes of each row, then the warps in warp order (same result layout as
+    // reduce_warps: thread t < 128 ends with row t & 15 of token t >> 4).
+    auto reduce_gemv = [&]() -> float {
+        float *rb = red_s + (redbuf * CW + warp) * 128;
+#pragma unroll
+        for (int tk = 0; tk < GTn; ++tk)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float v = acc2[tk][j].x + acc2[tk][j].y;
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                if (cch == 0) rb[tk * 16 + 4 * j + rsub] = v;
+            }
+        consumer_bar_n<CT>();
+        float v = 0.0f;
+        if (tid < 16 * GTn) {
+            const float *r0 = red_s + redbuf * CW * 128 + tid;
+            v = r0[0];
+#pragma unroll
+            for (int w = 1; w < CW; ++w) v += r0[w * 128];
         }
         redbuf ^= 1;
         return v;
@@ -366,19 +493,29 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     const int PR = p.part_rows;
 
     for (int t = 0; t < ntile; ++t) {
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
         const int slot = slot_of(t);
         const int pad = tpad(tcnt(t)), cols = kStageBytes / (pad * 128);
-        for (int b0 = 0; b0 < kbox; b0 += cols) run_item(b0, min(cols, kbox - b0), slot, pad);
-        const float v = reduce_warps();
+        float v;
+        if constexpr (GT > 0) {
+#pragma unroll
+            for (int tk = 0; tk < GTn; ++tk)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc2[tk][j] = make_float2(0.0f, 0.0f);
+            for (int b0 = 0; b0 < kbox; b0 += cols) run_item_gemv(b0, min(cols, kbox - b0), slot, pad);
+            v = reduce_gemv();
+        } else {
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+            for (int b0 = 0; b0 < kbox; b0 += cols) run_item(b0, min(cols, kbox - b0), slot, pad);
+            v = reduce_warps();
+        }
         if (tid < 128 && tok_t < p.m) part_s[tok_t * PR + t * kGroupRows + row_t] = v;
     }
     WS_MARK(2);
-    consumer_bar();  // part_s complete
+    consumer_bar_n<CT>();  // part_s complete
 
     // Visit every (token, valid row) of this CTA: fn(tok, global row, value index in part_s).
     auto for_rows = [&](auto fn) {
-        for (int i = tid; i < ntile * p.m * kGroupRows; i += kConsumerThreads) {
+        for (int i = tid; i < ntile * p.m * kGroupRows; i += CT) {
             const int t = i / (p.m * kGroupRows), j = i - t * (p.m * kGroupRows);
             const int tok = j >> 4, r = j & 15;
             if (r < tcnt(t)) fn(tok, trow(t) + r, tok * PR + t * kGroupRows + r);
@@ -399,7 +536,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
             float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
             for_rows([&](int tok, int row, int pi) { dst[(size_t)tok * p.n + row] = part_s[pi]; });
         }
-        consumer_bar();  // the st.release.sys below is cumulative over the stores this barrier ordered
+        consumer_bar_n<CT>();  // the st.release.sys below is cumulative over the stores this barrier ordered
         if (tid < p.world) {
             uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[tid] + p.lay.flags_off) +
                           ((size_t)bank * p.world + X.rank) * nflag;
@@ -407,7 +544,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
             // wait for the same CTA of every rank, then fold in rank order
             wait_flag(myflags + (size_t)tid * nflag + cta, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
         }
-        consumer_bar();
+        consumer_bar_n<CT>();
         const float *slots = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.slota_off) +
                              (size_t)bank * p.world * astride;
         for_rows([&](int tok, int row, int) {
@@ -427,7 +564,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
             for_rows([&](int tok, int row, int pi) { dst[(size_t)tok * p.lay.max_vocab + A.vocab_row0 + row] = part_s[pi]; });
         }
     }
-    for (int tok = warp; tok < p.m; tok += kConsumerWarps) {  // a warp per token
+    for (int tok = warp; tok < p.m; tok += CW) {  // a warp per token
         float bv = -INFINITY;
         uint32_t bi = 0xFFFFFFFFu;
         for (int i = lane; i < ntile * kGroupRows; i += 32) {
@@ -449,7 +586,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
             *dst = ((uint64_t)__float_as_uint(bv) << 32) | bi;
         }
     }
-    consumer_bar();  // the st.release.sys below is cumulative over the stores this barrier ordered
+    consumer_bar_n<CT>();  // the st.release.sys below is cumulative over the stores this barrier ordered
     if (tid < p.world) {
         uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[tid] + p.lay.flags_off) +
                       ((size_t)bank * p.world + X.rank) * nflag;
@@ -458,22 +595,22 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     const bool copies = p.gather_logits && A.logits != nullptr;
     if (!copies && cta != 0) return;
     // every CTA of every rank has published (its flag follows all of its stores)
-    for (int i = tid; i < p.world * ncta; i += kConsumerThreads)
+    for (int i = tid; i < p.world * ncta; i += CT)
         wait_flag(myflags + (size_t)(i / ncta) * nflag + (i % ncta), seq, p.timeout_ns, X.status, kStatTimeoutGather);
-    consumer_bar();
+    consumer_bar_n<CT>();
     if (copies) {
         const float *gl = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.gather_off) +
                           (size_t)bank * p.lay.max_m * (size_t)p.lay.max_vocab;
         const int64_t per = ((int64_t)p.vocab + ncta - 1) / ncta;
         const int64_t v0 = (int64_t)cta * per, v1 = min((int64_t)p.vocab, v0 + per);
         for (int tok = 0; tok < p.m; ++tok)
-            for (int64_t v = v0 + tid; v < v1; v += kConsumerThreads)
+            for (int64_t v = v0 + tid; v < v1; v += CT)
                 A.logits[(size_t)tok * p.vocab + v] = __ldcg(gl + (size_t)tok * p.lay.max_vocab + v);
     }
     if (cta == 0 && A.argmax != nullptr) {
         const uint64_t *pairs = reinterpret_cast<const uint64_t *>(X.sym[X.rank] + p.lay.pairs_off) +
                                 (size_t)bank * p.world * kMaxCtas * p.lay.max_m;
-        for (int tok = warp; tok < p.m; tok += kConsumerWarps) {
+        for (int tok = warp; tok < p.m; tok += CW) {
             float bv = -INFINITY;
             uint32_t bi = 0xFFFFFFFFu;
             for (int i = lane; i < p.world * ncta; i += 32) {
@@ -493,9 +630,10 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) fp8_rowpar_kernel(const __grid_constant__ Fp8Params p) {
+template <int GT>
+__global__ void __launch_bounds__(fp8_threads(GT), 1) fp8_rowpar_kernel(const __grid_constant__ Fp8Params p) {
     const RankCtx &X = p.r[blockIdx.y].ctx;
-    fp8_rowpar_kernel_body(p);
+    fp8_rowpar_kernel_body<GT>(p);
     if (p.world > 1 || p.mode == kModeLmHead) {  // a lone all-reduce rank exchanges nothing
         // step_begin again: the value is unchanged until the last CTA publishes the next one below
         step_end(X, step_begin(X), gridDim.x);
