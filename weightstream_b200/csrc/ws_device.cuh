@@ -212,19 +212,24 @@ __device__ __forceinline__ float2 f16x2_to_f32x2(uint32_t v) {
     asm("{.reg .f16 l, h; mov.b32 {l, h}, %2; cvt.f32.f16 %0, l; cvt.f32.f16 %1, h;}" : "=f"(r.x), "=f"(r.y) : "r"(v));
     return r;
 }
-// Two E4M3 bytes -> two f32: the low (H = 0) or high (H = 1) half of v.
+// Two E4M3 bytes, the low (H = 0) or high (H = 1) half of v, -> f16x2 (exact).  The half is
+// named by a register unpack so that the conversion can take it as an operand modifier.
 template <int H>
-__device__ __forceinline__ float2 e4m3x2_to_f32x2(uint32_t v) {
-    uint32_t h;
-    if (H == 0) asm("{.reg .b16 l, h; mov.b32 {l, h}, %1; cvt.rn.f16x2.e4m3x2 %0, l;}" : "=r"(h) : "r"(v));
-    else        asm("{.reg .b16 l, h; mov.b32 {l, h}, %1; cvt.rn.f16x2.e4m3x2 %0, h;}" : "=r"(h) : "r"(v));
-    return f16x2_to_f32x2(h);
+__device__ __forceinline__ uint32_t e4m3x2_half_to_f16x2(uint32_t v) {
+    uint32_t r;
+    if (H == 0) asm("{.reg .b16 l, h; mov.b32 {l, h}, %1; cvt.rn.f16x2.e4m3x2 %0, l;}" : "=r"(r) : "r"(v));
+    else        asm("{.reg .b16 l, h; mov.b32 {l, h}, %1; cvt.rn.f16x2.e4m3x2 %0, h;}" : "=r"(r) : "r"(v));
+    return r;
 }
-// (s.x, s.y) += (a.x * b.x, a.y * b.y): one packed fp32 FMA (two lanes' worth of work per issue slot).
-__device__ __forceinline__ void fma_f32x2(float2 &s, float2 a, float2 b) {
-    asm("{.reg .b64 ra, rb, rc; mov.b64 ra, {%2, %3}; mov.b64 rb, {%4, %5}; mov.b64 rc, {%0, %1};"
-        " fma.rn.f32x2 rc, ra, rb, rc; mov.b64 {%0, %1}, rc;}"
-        : "+f"(s.x), "+f"(s.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+// Two E2M1 codes, byte B of v (low nibble -> low half), -> f16x2 (exact).
+template <int B>
+__device__ __forceinline__ uint32_t e2m1x2_byte_to_f16x2(uint32_t v) {
+    uint32_t r;
+    if (B == 0) asm("{.reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %1; cvt.rn.f16x2.e2m1x2 %0, b0;}" : "=r"(r) : "r"(v));
+    if (B == 1) asm("{.reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %1; cvt.rn.f16x2.e2m1x2 %0, b1;}" : "=r"(r) : "r"(v));
+    if (B == 2) asm("{.reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %1; cvt.rn.f16x2.e2m1x2 %0, b2;}" : "=r"(r) : "r"(v));
+    if (B == 3) asm("{.reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %1; cvt.rn.f16x2.e2m1x2 %0, b3;}" : "=r"(r) : "r"(v));
+    return r;
 }
 // s += a.lo * b.lo + a.hi * b.hi with f16 operands and fp32 accumulation: the products of two
 // 4-significant-bit values are exact, every add rounds once in fp32.

@@ -70,10 +70,10 @@ struct alignas(64) Fp8Params {
     Fp8RankArgs r[WS_MAX_WORLD];
 };
 
-// Consumer warps per CTA: the tensor-core formulation is bound by the MMA issue rate and gains
-// nothing from more warps; the CUDA-core one needs the extra warps to cover load and FMA latency.
+// Consumer warps per CTA.  Sixteen warps instead of eight changed neither formulation's time by
+// more than 2 % on B200, so both run eight.
 #ifndef WS_GEMV_WARPS
-#define WS_GEMV_WARPS 16
+#define WS_GEMV_WARPS 8
 #endif
 __host__ __device__ constexpr int fp8_consumer_warps(int gt) { return gt > 0 ? WS_GEMV_WARPS : kConsumerWarps; }
 __host__ __device__ constexpr int fp8_threads(int gt) { return (fp8_consumer_warps(gt) + 1) * 32; }  // + the TMA producer warp
@@ -389,29 +389,31 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     };
 
     // ---- CUDA-core formulation.  Lane = (row 4j + rsub of the tile, 16-byte chunk cch of the box);
-    // acc2[tok][j] collects this lane's share of row 4j + rsub (even / odd elements) over every box
-    // its warp visits.  The block scale (activation x weight) is folded into the activation operand
-    // once per box, so the inner loop is conversions and packed FMAs only.
+    // accv[tok][j] collects this lane's share of row 4j + rsub over every box its warp visits.
+    // Weights become f16 pairs, the activations are kept as f16 pairs, their exact products are
+    // summed in fp32 by mixed-precision FMAs (measured: 45 weight bytes per clock and SM, against
+    // 31 with conversions to f32 and packed fp32 FMAs), and the block scale multiplies each
+    // 16-element partial sum.
     constexpr int GTn = GT > 0 ? GT : 1;
-    float2 acc2[GTn][4];
+    float accv[GTn][4];
     const int rsub = lane >> 3, cch = lane & 7;
     // whole tiles: row 4j + rsub sits at j * 512 + its swizzled chunk; the swizzle phase (row & 7)
     // only depends on the parity of j
     const uint32_t off_e = (uint32_t)(rsub * 128 + ((cch ^ rsub) << 4));
     const uint32_t off_o = (uint32_t)((rsub + 4) * 128 + ((cch ^ rsub ^ 4) << 4));
-    auto dot16 = [&](const uint4 w, const float2 (&xf)[GTn][8], int j) {
-        const float2 w0 = e4m3x2_to_f32x2<0>(w.x), w1 = e4m3x2_to_f32x2<1>(w.x);
-        const float2 w2 = e4m3x2_to_f32x2<0>(w.y), w3 = e4m3x2_to_f32x2<1>(w.y);
-        const float2 w4 = e4m3x2_to_f32x2<0>(w.z), w5 = e4m3x2_to_f32x2<1>(w.z);
-        const float2 w6 = e4m3x2_to_f32x2<0>(w.w), w7 = e4m3x2_to_f32x2<1>(w.w);
+    auto dot16 = [&](const uint4 w, const uint32_t (&xh)[GTn][8], const float (&f)[GTn], int j) {
+        const uint32_t h0 = e4m3x2_half_to_f16x2<0>(w.x), h1 = e4m3x2_half_to_f16x2<1>(w.x);
+        const uint32_t h2 = e4m3x2_half_to_f16x2<0>(w.y), h3 = e4m3x2_half_to_f16x2<1>(w.y);
+        const uint32_t h4 = e4m3x2_half_to_f16x2<0>(w.z), h5 = e4m3x2_half_to_f16x2<1>(w.z);
+        const uint32_t h6 = e4m3x2_half_to_f16x2<0>(w.w), h7 = e4m3x2_half_to_f16x2<1>(w.w);
 #pragma unroll
         for (int tk = 0; tk < GTn; ++tk) {
-            float2 a = acc2[tk][j];
-            fma_f32x2(a, w0, xf[tk][0]); fma_f32x2(a, w1, xf[tk][1]);
-            fma_f32x2(a, w2, xf[tk][2]); fma_f32x2(a, w3, xf[tk][3]);
-            fma_f32x2(a, w4, xf[tk][4]); fma_f32x2(a, w5, xf[tk][5]);
-            fma_f32x2(a, w6, xf[tk][6]); fma_f32x2(a, w7, xf[tk][7]);
-            acc2[tk][j] = a;
+            float s0 = 0.0f, s1 = 0.0f;
+            fma2_f16(s0, h0, xh[tk][0]); fma2_f16(s1, h1, xh[tk][1]);
+            fma2_f16(s0, h2, xh[tk][2]); fma2_f16(s1, h3, xh[tk][3]);
+            fma2_f16(s0, h4, xh[tk][4]); fma2_f16(s1, h5, xh[tk][5]);
+            fma2_f16(s0, h6, xh[tk][6]); fma2_f16(s1, h7, xh[tk][7]);
+            accv[tk][j] = fmaf(s0 + s1, f[tk], accv[tk][j]);
         }
     };
     auto run_item_gemv = [&](int b0, int nb, int slot, int pad) {
@@ -426,33 +428,30 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
             const int box = b0 + bi;
             const int kb = box * 4 + (cch >> 1);  // the 32-wide K block of this lane's chunk
             const float sw = kb < kb32 ? lds_f32(swrow + (uint32_t)(((kofs + kb * 32) >> p.bk_shift) * 4)) : 0.0f;
-            float2 xf[GTn][8];
+            uint32_t xh[GTn][8];
+            float f[GTn];
 #pragma unroll
             for (int tk = 0; tk < GTn; ++tk) {
                 const uint32_t xa = xbase + (uint32_t)((tk * kbox + box) * 256);
                 const uint4 x0 = lds_u128(xa), x1 = lds_u128(xa + 16);
-                const float f = kb < kb32 ? lds_f32(smem_u32(sa_s) + (uint32_t)((kb * 8 + tk) * 4)) * sw : 0.0f;
-                const uint32_t xh[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float2 v = f16x2_to_f32x2(xh[i]);
-                    xf[tk][i] = make_float2(v.x * f, v.y * f);
-                }
+                xh[tk][0] = x0.x; xh[tk][1] = x0.y; xh[tk][2] = x0.z; xh[tk][3] = x0.w;
+                xh[tk][4] = x1.x; xh[tk][5] = x1.y; xh[tk][6] = x1.z; xh[tk][7] = x1.w;
+                f[tk] = kb < kb32 ? lds_f32(smem_u32(sa_s) + (uint32_t)((kb * 8 + tk) * 4)) * sw : 0.0f;
             }
             const uint32_t bbase = sbase + bi * pad * 128;
             if (pad == kGroupRows) {  // whole tile: four rows per lane, straight-line
                 const uint4 wa = lds_u128(bbase + off_e), wb = lds_u128(bbase + off_o);
                 const uint4 wc = lds_u128(bbase + 1024 + off_e), wd = lds_u128(bbase + 1024 + off_o);
-                dot16(wa, xf, 0);
-                dot16(wb, xf, 1);
-                dot16(wc, xf, 2);
-                dot16(wd, xf, 3);
+                dot16(wa, xh, f, 0);
+                dot16(wb, xh, f, 1);
+                dot16(wc, xh, f, 2);
+                dot16(wd, xh, f, 3);
             } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     if (4 * j < pad) {  // warp-uniform: rows the stage holds
                         const int r = 4 * j + rsub;
-                        dot16(lds_u128(bbase + r * 128 + ((uint32_t)(cch ^ ((bi * pad + r) & 7)) << 4)), xf, j);
+                        dot16(lds_u128(bbase + r * 128 + ((uint32_t)(cch ^ ((bi * pad + r) & 7)) << 4)), xh, f, j);
                     }
                 }
             }
@@ -470,7 +469,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         for (int tk = 0; tk < GTn; ++tk)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                float v = acc2[tk][j].x + acc2[tk][j].y;
+                float v = accv[tk][j];
                 v += __shfl_xor_sync(0xffffffffu, v, 1);
                 v += __shfl_xor_sync(0xffffffffu, v, 2);
                 v += __shfl_xor_sync(0xffffffffu, v, 4);
@@ -498,9 +497,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         float v;
         if constexpr (GT > 0) {
 #pragma unroll
-            for (int tk = 0; tk < GTn; ++tk)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc2[tk][j] = make_float2(0.0f, 0.0f);
+            for (int tk = 0; tk < GTn; ++tk) accv[tk][0] = accv[tk][1] = accv[tk][2] = accv[tk][3] = 0.0f;
             for (int b0 = 0; b0 < kbox; b0 += cols) run_item_gemv(b0, min(cols, kbox - b0), slot, pad);
             v = reduce_gemv();
         } else {

@@ -16,8 +16,9 @@
 //                     (TMA, 128B swizzle), their UE8M0 scale bytes and the pass's activations
 //                     (bulk copies) into shared-memory rings.  Sixteen consumer warps: a lane owns
 //                     one 32-wide K block (16 bytes of E2M1 codes) of every row its warp visits,
-//                     keeps that block's activations in registers for the whole pass, converts
-//                     the codes to f32 pairs and accumulates with packed fp32 FMAs; a row's
+//                     keeps that block's activations in registers (f16 pairs) for the whole pass,
+//                     converts the codes to f16 pairs and accumulates the exact products in fp32
+//                     (fma.rn.f32.f16); a row's
 //                     lanes are combined by shuffles and lane 0 adds the result to the
 //                     accumulator of (K slice, token, row), which only ever this warp touches:
 //                     no barrier between passes, deterministic order.
@@ -30,6 +31,7 @@
 
 #include "ws_device.cuh"
 #include "ws_moe_kernel.cuh"  // kMoeMaxRoutes, kMoeMaxExperts, e8m0_f32
+#include "ws_fp8_kernel.cuh"  // WS_MARK2 (probe builds only)
 
 namespace ws {
 
@@ -211,22 +213,21 @@ __host__ __device__ inline void moe_gemv_rows(int n, int gran, int ncta, int cta
     b = gran * (int)((int64_t)(cta + 1) * U / ncta);
 }
 
-// 16 bytes of E2M1 codes (32 values, low nibble first) times 32 activations (16 f32 pairs).
-__device__ __forceinline__ float dot32_e2m1(const uint4 w, const float2 (&xf)[16]) {
-    float2 s0 = make_float2(0.0f, 0.0f), s1 = make_float2(0.0f, 0.0f);
+// 16 bytes of E2M1 codes (32 values, low nibble first) times 32 activations (16 f16 pairs):
+// the codes become f16 pairs, the products of a 2-bit and a 4-bit significand are exact, the
+// sums are fp32 (mixed-precision FMA).  Measured on B200: 28 weight bytes per clock and SM,
+// against 16 with conversions to f32 and packed fp32 FMAs.
+__device__ __forceinline__ float dot32_e2m1(const uint4 w, const uint32_t (&xh)[16]) {
+    float s0 = 0.0f, s1 = 0.0f;
     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float2 a = f16x2_to_f32x2(e2m1x2_to_f16x2(ww[i]));
-        const float2 b = f16x2_to_f32x2(e2m1x2_to_f16x2(ww[i] >> 8));
-        const float2 c = f16x2_to_f32x2(e2m1x2_to_f16x2(ww[i] >> 16));
-        const float2 d = f16x2_to_f32x2(e2m1x2_to_f16x2(ww[i] >> 24));
-        fma_f32x2(s0, a, xf[4 * i + 0]);
-        fma_f32x2(s1, b, xf[4 * i + 1]);
-        fma_f32x2(s0, c, xf[4 * i + 2]);
-        fma_f32x2(s1, d, xf[4 * i + 3]);
+        fma2_f16(s0, e2m1x2_byte_to_f16x2<0>(ww[i]), xh[4 * i + 0]);
+        fma2_f16(s1, e2m1x2_byte_to_f16x2<1>(ww[i]), xh[4 * i + 1]);
+        fma2_f16(s0, e2m1x2_byte_to_f16x2<2>(ww[i]), xh[4 * i + 2]);
+        fma2_f16(s1, e2m1x2_byte_to_f16x2<3>(ww[i]), xh[4 * i + 3]);
     }
-    return (s0.x + s0.y) + (s1.x + s1.y);
+    return s0 + s1;
 }
 
 __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
@@ -274,6 +275,7 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
     // pass table, activations and the step sequence come from earlier work on the stream
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t seq = step_begin(X);
+    if (tid == 0) WS_MARK2(2);
     const int NP = *reinterpret_cast<const int32_t *>(A.work + W.hdr);
     {
         const uint2 *src = reinterpret_cast<const uint2 *>(A.work + W.pass);
@@ -364,35 +366,31 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
                 const int xs = xi % kMoeXSlots;
                 const int route = sorted_s[P.first + j];
                 const int tok = route / p.top_k;
+                if (tid == 0 && j == 0) WS_MARK2(8 + ps * 4 + 0);
                 mbar_wait(xfull0 + xs * 8, ((uint32_t)(xi / kMoeXSlots)) & 1u, X.status);
-                // this lane's 32 activations, scaled by their block scale, as f32 pairs
-                float2 xf[16];
-                {
-                    const uint32_t xa = xring0 + xs * S.xbytes;
-                    const float sa = lvalid ? lds_f32(xa + p.k * 2 + cs * 4) : 0.0f;
+                if (tid == 0 && j == 0) WS_MARK2(8 + ps * 4 + 1);
+                // this lane's 32 quantised activations (f16 pairs) and their block scale
+                uint32_t xh[16];
+                const uint32_t xa = xring0 + xs * S.xbytes;
+                const float sa = lvalid ? lds_f32(xa + p.k * 2 + cs * 4) : 0.0f;
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const uint4 v = lds_u128(xa + cs * 64 + q * 16);
-                        const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float2 f = f16x2_to_f32x2(vv[i]);
-                            xf[q * 4 + i] = make_float2(f.x * sa, f.y * sa);
-                        }
-                    }
+                for (int q = 0; q < 4; ++q) {
+                    const uint4 v = lds_u128(xa + cs * 64 + q * 16);
+                    xh[q * 4 + 0] = v.x; xh[q * 4 + 1] = v.y; xh[q * 4 + 2] = v.z; xh[q * 4 + 3] = v.w;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(xempty0 + xs * 8);  // the values are in registers
                 if (!landed) {
                     mbar_wait(full0 + s * 8, ((uint32_t)(item / NS)) & 1u, X.status);
                     landed = true;
+                    if (tid == 0) WS_MARK2(8 + ps * 4 + 2);
                 }
                 if (wactive) {
                     float *acc = acc_base + ((size_t)kslice * p.m + tok) * acc_stride + r0;
                     for (int r = rg; r < rows; r += ng) {
                         const uint4 w = lds_u128(sbase + lane_col + r * 128 + ((uint32_t)(cc ^ (r & 7)) << 4));
                         const uint32_t sb = lds_u8(sbase + p.scale_off + r * kb32 + cs);
-                        float v = dot32_e2m1(w, xf) * (lvalid ? e8m0_f32(sb) : 0.0f);
+                        float v = dot32_e2m1(w, xh) * (sa * e8m0_f32(sb));
 #pragma unroll
                         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
                         if (lane == 0) atomicAdd(acc + r, v);  // only this warp ever adds to this address
@@ -401,9 +399,12 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + s * 8);
+            if (tid == 0) WS_MARK2(8 + ps * 4 + 3);
         }
     }
+    if (tid == 0) WS_MARK2(1);
     consumer_bar_n<CT>();  // accumulators complete
+    if (tid == 0) WS_MARK2(3);
 
     // Value of (token, row r of this CTA): the K slices in ascending order.
     auto value = [&](int tok, int r) {
