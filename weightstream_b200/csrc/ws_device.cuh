@@ -41,7 +41,7 @@ struct SymLayout {
     int64_t flags_off;   // u32  [2 banks][R src][kMaxCtas + kMaxShared]
     int64_t pairs_off;   // u64  [2][R][kMaxCtas][max_m]      (argmax candidates)
     int64_t slotb_off;   // f32  [2][R][kMaxShared][8*16... sized max_m*16]
-    int64_t slota_off;   // f32  [2][R][max_m*max_n]
+    int64_t slota_off;   // u64  [2][R][max_m*max_n]  {step sequence, fp32 bits} words of the all-reduce
     int64_t gather_off;  // f32  [2][max_m*max_vocab]
     int64_t total;
     int32_t max_m, max_n, max_vocab, world;
@@ -56,7 +56,7 @@ __host__ inline SymLayout make_layout(int world, int max_m, int max_n, int max_v
     L.flags_off = o;  o += align_up((int64_t)2 * world * (kMaxCtas + kMaxShared) * 4, 256);
     L.pairs_off = o;  o += align_up((int64_t)2 * world * kMaxCtas * max_m * 8, 256);
     L.slotb_off = o;  o += align_up((int64_t)2 * world * kMaxShared * max_m * kGroupRows * 4, 256);
-    L.slota_off = o;  o += align_up((int64_t)2 * world * max_m * max_n * 4, 256);
+    L.slota_off = o;  o += align_up((int64_t)2 * world * max_m * max_n * 8, 256);
     L.gather_off = o; o += align_up((int64_t)2 * max_m * (int64_t)max_vocab * 4, 256);
     L.total = o;
     return L;
@@ -283,6 +283,37 @@ __device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t seq, ui
             return false;
         }
         if (*(volatile uint32_t *)status != 0u) return false;  // someone else already failed
+    }
+}
+
+// All-reduce words.  A partial sum travels as one 64-bit word {step sequence, fp32 bits}; a
+// naturally aligned 64-bit store is single-copy atomic, so the value and its tag arrive together
+// and the receiver needs neither a fence on the sender nor a separate flag: it polls the word
+// until the tag is this step's.  One NVLink store latency instead of store, fence, flag.
+__device__ __forceinline__ void st_word_sys(uint64_t *p, uint32_t seq, float v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(((uint64_t)seq << 32) | __float_as_uint(v)) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_word_sys(const uint64_t *p) {
+    uint64_t v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+// Bounded like wait_flag; returns 0 when the wait gave up (the status word then says so).
+__device__ __forceinline__ float wait_word(const uint64_t *p, uint32_t seq, uint64_t timeout_ns, uint32_t *status,
+                                           uint32_t code) {
+    uint64_t w = ld_word_sys(p);
+    if ((uint32_t)(w >> 32) == seq) return __uint_as_float((uint32_t)w);
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        for (int i = 0; i < 32; ++i) {
+            w = ld_word_sys(p);
+            if ((uint32_t)(w >> 32) == seq) return __uint_as_float((uint32_t)w);
+        }
+        if (globaltimer_ns() - t0 > timeout_ns) {
+            atomicCAS(status, 0u, code | (uint32_t)(-WS_ERR_TIMEOUT));
+            return 0.0f;
+        }
+        if (*(volatile uint32_t *)status != 0u) return 0.0f;  // someone else already failed
     }
 }
 

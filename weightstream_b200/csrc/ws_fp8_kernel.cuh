@@ -16,9 +16,9 @@
 //     Its issue rate caps streaming near 70 % of HBM bandwidth, which is why it is not used
 //     for the narrow cases.
 //
-// Exchange (world > 1): a CTA stores its rows' fp32 partials into slot [my rank] of every
-// peer's exchange memory and then releases one flag per peer; it waits for the same CTA of
-// every rank and adds the slots in rank order, so all ranks produce identical bits.
+// Exchange (world > 1): a thread stores its rows' fp32 partials into slot [my rank] of every
+// peer's exchange memory as 64-bit {step, value} words and then adds the same rows' words of all
+// ranks in rank order as they arrive, so all ranks produce identical bits.
 //
 // lm_head mode: rows are vocabulary entries; instead of a sum every rank's rows are gathered
 // (stored into every peer's logits buffer) and each CTA publishes its best (value, lowest
@@ -528,26 +528,20 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
                               (size_t)bank * p.world * nflag;
 
     if (p.mode == kModeAllReduce) {
+        // every thread sends its rows' partials to all ranks as tagged words, then folds the same
+        // rows in rank order as the ranks' words arrive: no barrier, fence or flag in between
         const size_t astride = (size_t)p.lay.max_m * p.lay.max_n;
         for (int pr = 0; pr < p.world; ++pr) {
-            float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
-            for_rows([&](int tok, int row, int pi) { dst[(size_t)tok * p.n + row] = part_s[pi]; });
+            uint64_t *dst = reinterpret_cast<uint64_t *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
+            for_rows([&](int tok, int row, int pi) { st_word_sys(dst + (size_t)tok * p.n + row, seq, part_s[pi]); });
         }
-        consumer_bar_n<CT>();  // the st.release.sys below is cumulative over the stores this barrier ordered
-        if (tid < p.world) {
-            uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[tid] + p.lay.flags_off) +
-                          ((size_t)bank * p.world + X.rank) * nflag;
-            st_release_sys(f + cta, seq);
-            // wait for the same CTA of every rank, then fold in rank order
-            wait_flag(myflags + (size_t)tid * nflag + cta, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-        }
-        consumer_bar_n<CT>();
-        const float *slots = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.slota_off) +
-                             (size_t)bank * p.world * astride;
+        const uint64_t *slots = reinterpret_cast<const uint64_t *>(X.sym[X.rank] + p.lay.slota_off) +
+                                (size_t)bank * p.world * astride;
         for_rows([&](int tok, int row, int) {
             const size_t off = (size_t)tok * p.n + row;
-            float s = __ldcg(slots + off);
-            for (int rr = 1; rr < p.world; ++rr) s += __ldcg(slots + rr * astride + off);
+            float s = wait_word(slots + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
+            for (int rr = 1; rr < p.world; ++rr)
+                s += wait_word(slots + rr * astride + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
             A.out[off] = s;
         });
         return;

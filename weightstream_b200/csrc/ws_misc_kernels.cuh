@@ -20,8 +20,7 @@ struct CollParams {
 };
 
 // One-shot all-reduce / all-gather: every rank stores its vector into slot [rank] of
-// every peer, releases one flag per CTA and peer, waits for the same CTA of every rank
-// and then adds (rank order 0..R-1, crates/weightstream-transport/src/ring.rs:399-408)
+// every peer and then adds (rank order 0..R-1, crates/weightstream-transport/src/ring.rs:399-408)
 // or concatenates (ring.rs:426-432) the slots.
 __device__ __forceinline__ void coll_body(const CollParams &p, const uint32_t seq) {
     const int vr = blockIdx.y, cta = blockIdx.x, ncta = gridDim.x, tid = threadIdx.x;
@@ -33,8 +32,22 @@ __device__ __forceinline__ void coll_body(const CollParams &p, const uint32_t se
         return;
     }
     const uint32_t bank = seq & 1u;
-    const int nflag = kMaxCtas + kMaxShared;
     const size_t astride = (size_t)p.lay.max_m * p.lay.max_n;
+    if (!p.gather) {  // all-reduce: tagged words, see st_word_sys
+        for (int pr = 0; pr < p.world; ++pr) {
+            uint64_t *dst = reinterpret_cast<uint64_t *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
+            for (int64_t i = a + tid; i < b; i += blockDim.x) st_word_sys(dst + i, seq, A.in[i]);
+        }
+        const uint64_t *slots = reinterpret_cast<const uint64_t *>(X.sym[X.rank] + p.lay.slota_off) + (size_t)bank * p.world * astride;
+        for (int64_t i = a + tid; i < b; i += blockDim.x) {
+            float s = wait_word(slots + i, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
+            for (int r = 1; r < p.world; ++r) s += wait_word(slots + r * astride + i, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
+            A.out[i] = s;
+        }
+        return;
+    }
+    // all-gather: plain stores into the (float-addressed) slots, one released flag per CTA and peer
+    const int nflag = kMaxCtas + kMaxShared;
     for (int pr = 0; pr < p.world; ++pr) {
         float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
         for (int64_t i = a + tid; i < b; i += blockDim.x) dst[i] = A.in[i];
@@ -48,16 +61,8 @@ __device__ __forceinline__ void coll_body(const CollParams &p, const uint32_t se
     if (tid < p.world) wait_flag(myflags + (size_t)tid * nflag + cta, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
     __syncthreads();
     const float *slots = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.slota_off) + (size_t)bank * p.world * astride;
-    if (p.gather) {
-        for (int r = 0; r < p.world; ++r)
-            for (int64_t i = a + tid; i < b; i += blockDim.x) A.out[(int64_t)r * p.len + i] = __ldcg(slots + r * astride + i);
-    } else {
-        for (int64_t i = a + tid; i < b; i += blockDim.x) {
-            float s = __ldcg(slots + i);
-            for (int r = 1; r < p.world; ++r) s += __ldcg(slots + r * astride + i);
-            A.out[i] = s;
-        }
-    }
+    for (int r = 0; r < p.world; ++r)
+        for (int64_t i = a + tid; i < b; i += blockDim.x) A.out[(int64_t)r * p.len + i] = __ldcg(slots + r * astride + i);
 }
 
 __global__ void __launch_bounds__(256) coll_kernel(const __grid_constant__ CollParams p) {

@@ -23,8 +23,8 @@
 //                     accumulator of (K slice, token, row), which only ever this warp touches:
 //                     no barrier between passes, deterministic order.
 //
-// Exchange: as in the FP8 kernel (partials stored to every peer, one released flag per CTA and
-// peer, fold in rank order).
+// Exchange: as in the FP8 kernel (partials stored to every peer as tagged words, folded in rank
+// order).
 #pragma once
 
 #include <math.h>
@@ -423,30 +423,22 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
         }
         return;
     }
+    // tagged-word exchange, as in the FP8 kernel: send, then fold the same rows in rank order
     const size_t astride = (size_t)p.lay.max_m * p.lay.max_n;
     for (int i = tid; i < p.m * rows_cta; i += CT) {
         const int tok = i / rows_cta, r = i - tok * rows_cta;
         const float v = value(tok, r);
         for (int pr = 0; pr < p.world; ++pr) {
-            float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
-            dst[(size_t)tok * p.n + row_a + r] = v;
+            uint64_t *dst = reinterpret_cast<uint64_t *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
+            st_word_sys(dst + (size_t)tok * p.n + row_a + r, seq, v);
         }
     }
-    consumer_bar_n<CT>();  // the st.release.sys below is cumulative over the stores this barrier ordered
-    if (tid < p.world) {
-        uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[tid] + p.lay.flags_off) + ((size_t)bank * p.world + X.rank) * nflag;
-        st_release_sys(f + cta, seq);
-        const uint32_t *myflags = reinterpret_cast<const uint32_t *>(X.sym[X.rank] + p.lay.flags_off) +
-                                  (size_t)bank * p.world * nflag;
-        wait_flag(myflags + (size_t)tid * nflag + cta, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-    }
-    consumer_bar_n<CT>();
-    const float *slots = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.slota_off) + (size_t)bank * p.world * astride;
+    const uint64_t *slots = reinterpret_cast<const uint64_t *>(X.sym[X.rank] + p.lay.slota_off) + (size_t)bank * p.world * astride;
     for (int i = tid; i < p.m * rows_cta; i += CT) {
         const int tok = i / rows_cta, r = i - tok * rows_cta;
         const size_t off = (size_t)tok * p.n + row_a + r;
-        float s = __ldcg(slots + off);
-        for (int rr = 1; rr < p.world; ++rr) s += __ldcg(slots + rr * astride + off);
+        float s = wait_word(slots + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
+        for (int rr = 1; rr < p.world; ++rr) s += wait_word(slots + rr * astride + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
         A.out[off] = s;
     }
 }
