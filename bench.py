@@ -313,24 +313,34 @@ def run_ours(args) -> None:
             for i in range(args.steps):
                 step(i)
 
-    def keep_busy(seconds: float):
+    # Every rank must run the same number of steps (a step cannot finish without its peers), so
+    # the length of the clock-sampling window is agreed on: one replay is timed, the slowest rank's
+    # time decides how many replays fill 0.8 s.
+    t_probe = time.perf_counter()
+    run_k_steps()
+    torch.cuda.synchronize()
+    t_probe = torch.tensor([time.perf_counter() - t_probe], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t_probe, op=dist.ReduceOp.MAX)
+    n_busy = int(min(20000, max(1, round(0.8 / max(float(t_probe.item()), 1e-6)))))
+
+    def keep_busy():
         """Same work, untimed, so that nvidia-smi (100 ms period) samples clocks under this load."""
-        t_end = time.perf_counter() + seconds
-        while time.perf_counter() < t_end:
+        for _ in range(n_busy):
             run_k_steps()
-            torch.cuda.synchronize()
+        torch.cuda.synchronize()
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    keep_busy(0.8)
+    keep_busy()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
     run_k_steps()               # the timed region: exactly K steps
     e1.record()
     barrier()
-    keep_busy(0.8)
+    keep_busy()
     ep.check()
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
