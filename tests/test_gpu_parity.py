@@ -94,6 +94,7 @@ FP8_CASES = [
     (512, 1024, "f32", 128, 128, (1, 2, 8, 13)),
     (5120, 2304, "ue8m0", 32, 32, (1,)),         # reference shared-expert w2 (docs/model-spec.md)
     (7168, 2048, "f32", 128, 128, (1, 5)),       # shared-expert down at the measured shape
+    (7168, 1024, "f32", 128, 128, (64, 37)),     # o_proj's K/8 shard: all 64 rows in one launch
 ]
 
 
@@ -106,7 +107,7 @@ def test_fp8_gemm_tp1(dev, tpmod, oracle, n, k, scale, bn, bk, ms, split, kernel
     w, sc = synth.fp8_weight(rng, n, k, scale=scale, bn=bn, bk=bk)
     if kernel == 2 and not split:
         pytest.skip("the leftover-row knob only exists in the mma.sync kernel")
-    ep = tpmod.Endpoint(max_m=16, max_n=max(n, 16))
+    ep = tpmod.Endpoint(max_m=max(16, max(ms)), max_n=max(n, 16))
     ep.set_split(split)
     ep.set_kernel(kernel)
     try:

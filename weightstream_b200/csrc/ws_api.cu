@@ -447,7 +447,23 @@ static ws_status_t umma_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_
     return WS_OK;
 }
 
-// One fused step over at most 8 activation rows.
+// Activation rows the next launch takes: up to 64 when their quantised copies fit in shared
+// memory beside at least three weight stages (the weights are then streamed once for all of
+// them), else 8.
+static int fp8_rows_per_launch(const ws_tp *t0, const ws_fp8_gemm_args_t &a, int ncta, int rem) {
+    if (rem <= 8 || t0->kernel_sel == 2) return std::min(rem, 8);
+    const int kbox = (a.k + 127) / 128;
+    const int Gm = a.n / kGroupRows / ncta;
+    const int skb = (int)((a.k0 + a.k - 1) / a.block_k - a.k0 / a.block_k + 1);
+    for (int mp = std::min(64, (rem + 7) / 8 * 8); mp > 8; mp -= 8) {
+        const int m = std::min(rem, mp);
+        const Fp8Smem fixed = fp8_smem_layout(0, kbox, mp, (Gm * kGroupRows) / a.block_n + 4, skb, m, (Gm + 2) * kGroupRows, 0);
+        if ((kSmemBudget - fixed.total) / kStageBytes >= 3) return m;
+    }
+    return 8;
+}
+
+// One fused step over the activation rows [m0, m0 + mt) (mt from fp8_rows_per_launch).
 static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t *args, const ws_lm_head_args_t *lm,
                             int m0, int mt, void *const *streams, int ncta, bool same_device) {
     ws_tp *t0 = ranks[0];
@@ -469,7 +485,7 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
     p.mode = lm ? kModeLmHead : kModeAllReduce;
     p.vocab = lm ? lm[0].vocab : 0;
     p.gather_logits = 0;
-    p.mp = mt <= 1 ? 1 : mt <= 2 ? 2 : mt <= 4 ? 4 : 8;
+    p.mp = mt <= 1 ? 1 : mt <= 2 ? 2 : mt <= 4 ? 4 : (mt + 7) / 8 * 8;
     p.timeout_ns = t0->timeout_ns;
     p.lay = t0->lay;
     const int kbox = (p.k + 127) / 128;
@@ -554,9 +570,11 @@ ws_status_t ws_fp8_rowpar_gemm_allreduce_group(ws_tp_t *const *ranks, int32_t n,
     if (args[0].m > t0->cfg.max_m || args[0].n > t0->cfg.max_n)
         return fail(t0, WS_ERR_CAPACITY, "m=%d n=%d exceed the endpoint's max_m=%d max_n=%d", args[0].m, args[0].n,
                     t0->cfg.max_m, t0->cfg.max_n);
-    for (int m0 = 0; m0 < args[0].m; m0 += 8) {
-        s = fp8_step(ranks, n, args, nullptr, m0, std::min(8, args[0].m - m0), streams, ncta, same);
+    for (int m0 = 0; m0 < args[0].m;) {
+        const int mt = fp8_rows_per_launch(t0, args[0], ncta, args[0].m - m0);
+        s = fp8_step(ranks, n, args, nullptr, m0, mt, streams, ncta, same);
         if (s != WS_OK) return s;
+        m0 += mt;
     }
     return WS_OK;
 }
@@ -591,9 +609,11 @@ ws_status_t ws_lm_head_allgather_argmax_group(ws_tp_t *const *ranks, int32_t n, 
     if (args[0].g.m > t0->cfg.max_m) return fail(t0, WS_ERR_CAPACITY, "m=%d exceeds max_m=%d", args[0].g.m, t0->cfg.max_m);
     if (any_logits && args[0].vocab > t0->cfg.max_vocab)
         return fail(t0, WS_ERR_CAPACITY, "vocab=%d exceeds the endpoint's max_vocab=%d", args[0].vocab, t0->cfg.max_vocab);
-    for (int m0 = 0; m0 < args[0].g.m; m0 += 8) {
-        s = fp8_step(ranks, n, nullptr, args, m0, std::min(8, args[0].g.m - m0), streams, ncta, same);
+    for (int m0 = 0; m0 < args[0].g.m;) {
+        const int mt = fp8_rows_per_launch(t0, args[0].g, ncta, args[0].g.m - m0);
+        s = fp8_step(ranks, n, nullptr, args, m0, mt, streams, ncta, same);
         if (s != WS_OK) return s;
+        m0 += mt;
     }
     return WS_OK;
 }

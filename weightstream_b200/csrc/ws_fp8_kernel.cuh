@@ -90,7 +90,7 @@ __host__ __device__ inline Fp8Smem fp8_smem_layout(int nstages, int kbox, int mp
     int o = 0;
     s.stages = o; o += nstages * kStageBytes;
     s.q = o;      o += gt > 0 ? kbox * 128 * 2 * gt : kbox * 4 * mp * 32;
-    s.sa = o;     o += kbox * 4 * 8 * 4;
+    s.sa = o;     o += kbox * 4 * (mp > 8 ? mp : 8) * 4;
     s.sw = o;     o += ((nslot_max * skb * 4 + 15) / 16) * 16;
     s.red = o;    o += 2 * fp8_consumer_warps(gt) * 128 * 4;
     s.part = o;   o += ((m * part_rows * 4 + 15) / 16) * 16;
@@ -227,7 +227,8 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     if (tid == 0) WS_MARK2(1);
     // Prologue: weight scales of the rows this CTA touches (loads issued first, stored last, so
     // their latency overlaps the activation loads), then the activation quantisation.
-    // q_s[kb][tok][32] holds E4M3 bytes, sa_s[kb][tok(8)] the block scale 2^e.
+    // q_s[kb][tok][32] holds E4M3 bytes, sa_s[kb][tok(sast)] the block scale 2^e.
+    const int sast = p.mp > 8 ? p.mp : 8;  // tokens per K block in sa_s
     const int64_t kcol0 = A.k0 >> p.bk_shift;
     const int64_t srow_lo = (A.row0 + (int64_t)cta * R.Gm * kGroupRows) >> p.bn_shift;
     const int nslotA = R.Gm ? (int)(((A.row0 + (int64_t)(cta + 1) * R.Gm * kGroupRows - 1) >> p.bn_shift) - srow_lo + 1) : 0;
@@ -256,8 +257,8 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
             pre[u] = i < nsw ? load_scale(i) : 0.0f;
         }
         if (tid == 0) WS_MARK2(2);
-        for (int i = tid; i < kbox * 4 * 8; i += CT)  // tokens the launch does not carry
-            if ((i & 7) >= p.mp) sa_s[i] = 0.0f;
+        for (int i = tid; i < kbox * 4 * sast; i += CT)  // tokens the launch does not carry
+            if ((i % sast) >= p.m) sa_s[i] = 0.0f;
         if (tid == 0) WS_MARK2(3);
         const int chunks_per_row = kbox * 16;  // 8-element chunks over the padded K
         const int total = p.mp * chunks_per_row;
@@ -293,7 +294,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
                         *reinterpret_cast<uint2 *>(q_s + ((size_t)(kb * p.mp + tok[u]) * 32 + (ch[u] & 3) * 8)) =
                             valid[u] ? make_uint2(lo, hi) : make_uint2(0u, 0u);
                     }
-                    if ((ch[u] & 3) == 0) sa_s[kb * 8 + tok[u]] = valid[u] ? pow2_f32(e) : 0.0f;
+                    if ((ch[u] & 3) == 0) sa_s[kb * sast + tok[u]] = valid[u] ? pow2_f32(e) : 0.0f;
                 }
             }
         }
@@ -319,10 +320,17 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
 
     const int kofs = (int)(A.k0 - kcol0 * p.bk);  // k0 modulo the scale block
     // shared-space addresses of this lane's operands of K block 0 (advanced per block below)
-    const uint32_t q_lane = smem_u32(q_s) + (uint32_t)(g * 32 + tq * 4);
+    // More than eight activation rows ("wide"): warp w takes rows 8w..8w+7 of the activations
+    // (MMA columns) for every box of a tile, so each warp owns a 16 x 8 block of the output and
+    // nothing is combined across warps; the weights are staged once for all rows.
+    const bool wide = p.mp > 8;
+    const int tg = wide ? warp : 0;                 // this warp's group of eight activation rows
+    const bool tg_active = !wide || tg * 8 < p.mp;
+    const uint32_t q_lane = smem_u32(q_s) + (uint32_t)((tg * 8 + g) * 32 + tq * 4);
     const uint32_t q_step = (uint32_t)(p.mp * 32);
-    const uint32_t sa_lane = smem_u32(sa_s) + (uint32_t)(tq * 8);
-    const bool has_b = g < p.mp;
+    const uint32_t sa_lane = smem_u32(sa_s) + (uint32_t)((tg * 8 + tq * 2) * 4);
+    const uint32_t sa_step = (uint32_t)(sast * 4);
+    const bool has_b = tg * 8 + g < p.mp;
     auto mma_step = [&](uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, int kb, uint32_t swrow) {
         uint32_t b0r = 0, b1r = 0;
         if (has_b) {
@@ -331,7 +339,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         }
         float d[4];
         mma_e4m3_16x8x32(d, a0, a1, a2, a3, b0r, b1r);
-        const float2 sa = lds_f32x2(sa_lane + kb * 32);
+        const float2 sa = lds_f32x2(sa_lane + kb * sa_step);
         const float sw = lds_f32(swrow + (uint32_t)(((kofs + kb * 32) >> p.bk_shift) * 4));
         const float f0 = sa.x * sw, f1 = sa.y * sw;
         acc[0] = fmaf(d[0], f0, acc[0]);
@@ -345,7 +353,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         if (item == 0) WS_MARK(4);
         const uint32_t sbase = stage0 + s * kStageBytes;
         const uint32_t swrow = smem_u32(sw_s) + (uint32_t)(slot * p.skb * 4);
-        for (int bi = warp; bi < nb; bi += CW) {
+        for (int bi = wide ? 0 : warp; bi < nb && tg_active; bi += wide ? 1 : CW) {
             const int box = b0 + bi;
             const uint32_t bbase = sbase + bi * pad * 128 + lm_row * 128;
             const uint32_t sw7 = (uint32_t)((bi * pad + lm_row) & 7);  // 128B-swizzle phase of this row's address
@@ -436,7 +444,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
                 const uint4 x0 = lds_u128(xa), x1 = lds_u128(xa + 16);
                 xh[tk][0] = x0.x; xh[tk][1] = x0.y; xh[tk][2] = x0.z; xh[tk][3] = x0.w;
                 xh[tk][4] = x1.x; xh[tk][5] = x1.y; xh[tk][6] = x1.z; xh[tk][7] = x1.w;
-                f[tk] = kb < kb32 ? lds_f32(smem_u32(sa_s) + (uint32_t)((kb * 8 + tk) * 4)) * sw : 0.0f;
+                f[tk] = kb < kb32 ? lds_f32(smem_u32(sa_s) + (uint32_t)((kb * sast + tk) * 4)) * sw : 0.0f;
             }
             const uint32_t bbase = sbase + bi * pad * 128;
             if (pad == kGroupRows) {  // whole tile: four rows per lane, straight-line
@@ -503,6 +511,18 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         } else {
             acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
             for (int b0 = 0; b0 < kbox; b0 += cols) run_item(b0, min(cols, kbox - b0), slot, pad);
+            if (wide) {  // the accumulator fragment is final: rows g, g + 8 x tokens 8 tg + 2 tq, + 1
+                const int tk0 = tg * 8 + 2 * tq;
+                if (tk0 < p.m) {
+                    part_s[tk0 * PR + t * kGroupRows + g] = acc[0];
+                    part_s[tk0 * PR + t * kGroupRows + g + 8] = acc[2];
+                }
+                if (tk0 + 1 < p.m) {
+                    part_s[(tk0 + 1) * PR + t * kGroupRows + g] = acc[1];
+                    part_s[(tk0 + 1) * PR + t * kGroupRows + g + 8] = acc[3];
+                }
+                continue;
+            }
             v = reduce_warps();
         }
         if (tid < 128 && tok_t < p.m) part_s[tok_t * PR + t * kGroupRows + row_t] = v;
