@@ -387,13 +387,32 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
                 }
                 if (wactive) {
                     float *acc = acc_base + ((size_t)kslice * p.m + tok) * acc_stride + r0;
-                    for (int r = rg; r < rows; r += ng) {
-                        const uint4 w = lds_u128(sbase + lane_col + r * 128 + ((uint32_t)(cc ^ (r & 7)) << 4));
-                        const uint32_t sb = lds_u8(sbase + p.scale_off + r * kb32 + cs);
-                        float v = dot32_e2m1(w, xh) * (sa * e8m0_f32(sb));
+                    // four rows at a time: their 32-lane sums are folded together (4 -> 2 -> 1
+                    // values per lane, then three plain steps), 6 shuffles instead of 20
+                    const bool hi16 = (lane & 16) != 0, hi8 = (lane & 8) != 0;
+                    const int jrow = (hi16 ? 2 : 0) + (hi8 ? 1 : 0);
+                    for (int rb = rg; rb < rows; rb += 4 * ng) {
+                        float v[4];
 #pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                        if (lane == 0) atomicAdd(acc + r, v);  // only this warp ever adds to this address
+                        for (int j = 0; j < 4; ++j) {
+                            const int r = rb + j * ng;
+                            v[j] = 0.0f;
+                            if (r < rows) {  // warp-uniform
+                                const uint4 w = lds_u128(sbase + lane_col + r * 128 + ((uint32_t)(cc ^ (r & 7)) << 4));
+                                const uint32_t sb = lds_u8(sbase + p.scale_off + r * kb32 + cs);
+                                v[j] = dot32_e2m1(w, xh) * (sa * e8m0_f32(sb));
+                            }
+                        }
+                        float k0 = hi16 ? v[2] : v[0], k1 = hi16 ? v[3] : v[1];
+                        k0 += __shfl_xor_sync(0xffffffffu, hi16 ? v[0] : v[2], 16);
+                        k1 += __shfl_xor_sync(0xffffffffu, hi16 ? v[1] : v[3], 16);
+                        float k = hi8 ? k1 : k0;
+                        k += __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k1, 8);
+                        k += __shfl_xor_sync(0xffffffffu, k, 4);
+                        k += __shfl_xor_sync(0xffffffffu, k, 2);
+                        k += __shfl_xor_sync(0xffffffffu, k, 1);
+                        const int r = rb + jrow * ng;
+                        if ((lane & 7) == 0 && r < rows) atomicAdd(acc + r, k);  // only this warp ever adds to this address
                     }
                 }
             }
