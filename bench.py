@@ -190,7 +190,7 @@ def build_workload(args, tp, synth, torch, dev, sh, l2_bytes):
     if wl == "lm_head":
         vocab, k = 129280, 7168
         v0, vl = sh.slice_of(vocab)
-        ep = tp.Endpoint(sh, dev.index, max_m=8, max_n=16, max_vocab=vocab, wait_ms=5000)
+        ep = tp.Endpoint(sh, dev.index, max_m=max(m, 8), max_n=16, max_vocab=vocab, wait_ms=5000)
         # one weight set: a vocab shard is far larger than L2 at every N (116 MB at N=8 is borderline: two sets there)
         sets = 2 if vl * k < 2 * l2_bytes else 1
         ws, scs, row0 = [], [], 0
@@ -378,9 +378,11 @@ def run_ours(args) -> None:
     if rank == 0:
         peak, peak_src = measured_peak_gbs()
         achieved = abytes / (us_per_step * 1e-6) / 1e9
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised
-        # under profiles/ (o_proj, one rank, M=1: the capture shows the algorithmic bytes and nothing more)
-        traffic = 58.87e6 if (args.workload == "o_proj" and world == 1 and m == 1) else None
+        # DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu captures
+        # summarised under profiles/ (one rank, M=1; each shows the algorithmic bytes and under 1 % more).
+        # The MoE figure depends on how many experts a step hits: the capture's ratio is applied.
+        captured = {"o_proj": 58.85e6, "lm_head": 934.7e6, "moe_down": abytes * (47.12 / 46.79)}
+        traffic = captured.get(args.workload) if (world == 1 and m == 1) else None
         if args.workload == "o_proj":
             cpu_us, cpu_n = time_oracle(1, 12.0, m)
             cpu = {"value": cpu_us, "unit": "us", "cores": 1, "kind": "port",

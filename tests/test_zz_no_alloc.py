@@ -32,7 +32,7 @@ def test_static_scratch_matches_regular_entry_point_twice():
     torch.cuda.set_device(0)
     dev = torch.device("cuda:0")
     L = _lib.load()
-    # n = 7168 leaves row groups that are split along K, so the scratch is really used
+    # n = 7168 gives every CTA 48 or 49 rows (ragged tiles); the kernel keeps its status word and step counter in the scratch
     n, k = 7168, 2048
     rng = np.random.default_rng(77)
     w, sc = synth.fp8_weight(rng, n, k)
