@@ -112,14 +112,14 @@ def make_cpu_inputs(seed: int, m: int):
     return w, sc, x
 
 
-def time_oracle(threads: int, budget_s: float, m: int = 1):
+def time_oracle(threads: int, span_s: float, m: int = 1):
     """Time the oracle port of the reference's CPU path on the full o_proj step."""
     from oracle import oracle as O
     O.build()
     w, sc, x = make_cpu_inputs(1234, m)
     O.fp8_gemv(w[:256], sc, x, bn=BN, bk=BK, threads=threads)  # warm the library
     times = []
-    t_end = time.perf_counter() + budget_s
+    t_end = time.perf_counter() + span_s
     while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 200):
         t0 = time.perf_counter()
         O.fp8_gemv(w, sc, x, bn=BN, bk=BK, threads=threads)
@@ -369,6 +369,39 @@ def run_ours(args) -> None:
     torch.cuda.synchronize()
     e2e_us = (time.perf_counter() - t0) / e2e_steps * 1e6
 
+    # The exchange alone (N > 1): this library's all-reduce of one step's partial sums against an
+    # NCCL all-reduce of the same buffer, both as eager launches on the current stream.  NCCL is the
+    # comparison baseline only; nothing on the fused path calls it.
+    exchange = None
+    if world > 1 and args.workload != "lm_head":
+        nfl = m * N_OUT
+        xin = torch.randn(nfl, device=dev)
+        xout, xn = torch.empty_like(xin), xin.clone()
+        reps = 200
+
+        def timed(fn):
+            for _ in range(10):
+                fn()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) * 1e3 / reps
+
+        ours_us = timed(lambda: ep.allreduce_(xin, xout))
+        ep.check()
+        nccl_us = timed(lambda: dist.all_reduce(xn))
+        ex = torch.tensor([ours_us, nccl_us], dtype=torch.float64, device=dev)
+        dist.all_reduce(ex, op=dist.ReduceOp.MAX)
+        ours_us, nccl_us = [float(v) for v in ex.tolist()]
+        sent = nfl * 8 * (world - 1)  # 64-bit words {step, value} stored to every peer
+        exchange = {"floats": nfl, "ours_us": ours_us, "nccl_allreduce_us": nccl_us,
+                    "nvlink_bytes_sent_per_rank": sent, "nvlink_gbs_per_rank": sent / (ours_us * 1e-6) / 1e9,
+                    "how": f"{reps} eager launches each, CUDA events, max over ranks"}
+
     vals = torch.tensor([ms_total, e2e_us, statistics.median(iso)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
@@ -405,6 +438,7 @@ def run_ours(args) -> None:
             "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches),
             "clocks": clocks,
+            "exchange": exchange,
         }
         print(json.dumps(line), flush=True)
     ep.close()

@@ -180,12 +180,17 @@ ws_status_t ws_fp8_rowpar_gemm_allreduce_host(ws_tp_t *tp, const ws_fp8_gemm_arg
 ws_status_t ws_act_quant_fp8(const void *x, int64_t ldx, int32_t x_dtype, int32_t m, int32_t k,
                              uint8_t *q, uint8_t *sexp, void *stream);
 
-/* Scheduling knob with no counterpart in the reference: 1 (default) cuts the output
- * row groups that do not divide evenly over the CTAs along K so that every SM streams
- * the same number of bytes; 0 hands each leftover group to one CTA whole. */
+/* Scheduling knob with no counterpart in the reference: 1 (default) deals the output rows
+ * that do not fill whole 16-row tiles on every CTA out row by row, so that every SM streams
+ * the same number of bytes; 0 hands each leftover tile to one CTA whole.  Bit 2 set
+ * (on = 4 or 5) turns programmatic dependent launch off. */
 ws_status_t ws_tp_set_split(ws_tp_t *tp, int32_t on);
-/* Kernel choice for the FP8 steps, also without counterpart in the reference: 0 (default)
- * automatic, 1 the mma.sync kernel, 2 the tcgen05 / tensor-memory kernel whenever the shape fits. */
+/* Kernel choice, also without counterpart in the reference.  0 (default) automatic: FP8 steps
+ * run one or two activation rows on CUDA cores and three or more through the tensor-core MMA,
+ * the MoE step runs its decode form (prep kernel + CUDA-core kernel).  1: the mma.sync
+ * formulation for every FP8 row count and the MMA form of the MoE step.  2: the tcgen05 /
+ * tensor-memory FP8 kernel whenever the shape fits it.  All choices give results within the same
+ * tolerance of the reference arithmetic; ranks of one group must make the same choice. */
 ws_status_t ws_tp_set_kernel(ws_tp_t *tp, int32_t which);
 
 /* ---- FP8 GEMM for callers that must not allocate ------------------------------------------

@@ -12,6 +12,10 @@ identity, run-ahead safety and the fail-stop rules can be tested with no GPU:
   ring.rs:488-499: a sequence number that is neither this step's nor an earlier one aborts);
 * all-reduce adds the slots left to right in rank order (ring.rs:399-408); all-gather
   concatenates them (ring.rs:426-432).
+
+``tagged=True`` restates the all-reduce the fused kernels use: no flag; every value travels
+as one 64-bit word {step sequence, fp32 bits} and the receiver polls each word until its tag is
+this step's.  Same rank order, same fail-stop rules, same two banks.
 """
 from __future__ import annotations
 
@@ -34,11 +38,12 @@ class RankMemory:
     def __init__(self, world: int, elems: int):
         self.slots = np.zeros((2, world, elems), dtype=np.float32)
         self.flags = np.zeros((2, world), dtype=np.uint32)
+        self.words = np.zeros((2, world, elems), dtype=np.uint64)  # tagged all-reduce words
 
 
 class SimGroup:
-    def __init__(self, world: int, elems: int, wait_s: float = 1.0):
-        self.world, self.elems, self.wait_s = world, elems, wait_s
+    def __init__(self, world: int, elems: int, wait_s: float = 1.0, tagged: bool = False):
+        self.world, self.elems, self.wait_s, self.tagged = world, elems, wait_s, tagged
         self.mem = [RankMemory(world, elems) for _ in range(world)]
         self.step = [0] * world
         # fault injection (host side only): drop[(src, dst)] = True loses src's message to dst
@@ -73,8 +78,41 @@ class SimGroup:
                                       f"(have {have} of {self.world}); fail-stop, aborting")
             time.sleep(0)
 
+    def _allreduce_tagged(self, rank: int, v: np.ndarray) -> np.ndarray:
+        n = v.size
+        if n == 0 or n > self.elems:
+            raise ValueError(f"collective input len {n} not in 1..={self.elems}")
+        self.step[rank] += 1
+        seq = self.step[rank]
+        bank = seq & 1
+        send_seq = self.seq_override.get(rank, seq)
+        word = (np.uint64(send_seq) << np.uint64(32)) | v.view(np.uint32).astype(np.uint64)
+        for p in range(self.world):
+            if not self.drop.get((rank, p)):
+                self.mem[p].words[bank, rank, :n] = word  # value and tag in one store
+        deadline = time.monotonic() + self.wait_s
+        mine = self.mem[rank].words[bank]
+        while True:
+            w = mine[:, :n].copy()
+            tags = (w >> np.uint64(32)).astype(np.uint32)
+            if np.all(tags == seq):
+                vals = (w & np.uint64(0xFFFFFFFF)).astype(np.uint32).view(np.float32)
+                acc = vals[0].copy()
+                for r in range(1, self.world):
+                    acc = (acc + vals[r]).astype(np.float32)
+                return acc
+            if np.any(tags > seq):
+                raise ExchangeOutOfSequence(f"collective out of sequence: got step {int(tags.max())} at step {seq} (fail-stop)")
+            if time.monotonic() >= deadline:
+                have = [r for r in range(self.world) if np.all(tags[r] == seq)]
+                raise ExchangeTimeout(f"all-reduce wait timeout after {int(self.wait_s * 1e3)} ms "
+                                      f"(have {have} of {self.world}); fail-stop, aborting")
+            time.sleep(0)
+
     def allreduce(self, rank: int, vec: np.ndarray) -> np.ndarray:
         v = np.ascontiguousarray(vec, dtype=np.float32)
+        if self.tagged:
+            return self._allreduce_tagged(rank, v)
         bank = self._exchange(rank, v)
         s = self.mem[rank].slots[bank]
         acc = s[0, :v.size].copy()

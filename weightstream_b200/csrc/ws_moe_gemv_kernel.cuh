@@ -29,6 +29,8 @@
 
 #include <math.h>
 
+#include <type_traits>
+
 #include "ws_device.cuh"
 #include "ws_moe_kernel.cuh"  // kMoeMaxRoutes, kMoeMaxExperts, e8m0_f32
 #include "ws_fp8_kernel.cuh"  // WS_MARK2 (probe builds only)
@@ -217,17 +219,39 @@ __host__ __device__ inline void moe_gemv_rows(int n, int gran, int ncta, int cta
 // the codes become f16 pairs, the products of a 2-bit and a 4-bit significand are exact, the
 // sums are fp32 (mixed-precision FMA).  Measured on B200: 28 weight bytes per clock and SM,
 // against 16 with conversions to f32 and packed fp32 FMAs.
-__device__ __forceinline__ float dot32_e2m1(const uint4 w, const uint32_t (&xh)[16]) {
-    float s0 = 0.0f, s1 = 0.0f;
+template <int RT>
+__device__ __forceinline__ void dot32_e2m1(const uint4 w, const uint32_t (&xa)[16], const uint32_t (&xb)[16], float &da,
+                                           float &db) {
+    float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        fma2_f16(s0, e2m1x2_byte_to_f16x2<0>(ww[i]), xh[4 * i + 0]);
-        fma2_f16(s1, e2m1x2_byte_to_f16x2<1>(ww[i]), xh[4 * i + 1]);
-        fma2_f16(s0, e2m1x2_byte_to_f16x2<2>(ww[i]), xh[4 * i + 2]);
-        fma2_f16(s1, e2m1x2_byte_to_f16x2<3>(ww[i]), xh[4 * i + 3]);
+        const uint32_t h0 = e2m1x2_byte_to_f16x2<0>(ww[i]), h1 = e2m1x2_byte_to_f16x2<1>(ww[i]);
+        const uint32_t h2 = e2m1x2_byte_to_f16x2<2>(ww[i]), h3 = e2m1x2_byte_to_f16x2<3>(ww[i]);
+        fma2_f16(a0, h0, xa[4 * i + 0]); fma2_f16(a1, h1, xa[4 * i + 1]);
+        fma2_f16(a0, h2, xa[4 * i + 2]); fma2_f16(a1, h3, xa[4 * i + 3]);
+        if (RT == 2) {  // a second route of the same expert shares the converted codes
+            fma2_f16(b0, h0, xb[4 * i + 0]); fma2_f16(b1, h1, xb[4 * i + 1]);
+            fma2_f16(b0, h2, xb[4 * i + 2]); fma2_f16(b1, h3, xb[4 * i + 3]);
+        }
     }
-    return s0 + s1;
+    da = a0 + a1;
+    db = b0 + b1;
+}
+
+// Four per-lane partial sums (one per row) -> their 32-lane sums: lanes are folded 4 -> 2 -> 1
+// values per lane, then three plain steps (6 shuffles instead of 20).  The lane with
+// (lane & 7) == 0 ends with the sum of row 2 * bit4(lane) + bit3(lane).
+__device__ __forceinline__ float fold4(const float (&v)[4], bool hi16, bool hi8) {
+    float k0 = hi16 ? v[2] : v[0], k1 = hi16 ? v[3] : v[1];
+    k0 += __shfl_xor_sync(0xffffffffu, hi16 ? v[0] : v[2], 16);
+    k1 += __shfl_xor_sync(0xffffffffu, hi16 ? v[1] : v[3], 16);
+    float k = hi8 ? k1 : k0;
+    k += __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k1, 8);
+    k += __shfl_xor_sync(0xffffffffu, k, 4);
+    k += __shfl_xor_sync(0xffffffffu, k, 2);
+    k += __shfl_xor_sync(0xffffffffu, k, 1);
+    return k;
 }
 
 __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
@@ -362,17 +386,15 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
             const int s = item % NS;
             const uint32_t sbase = stage0 + s * p.stage_bytes;
             bool landed = false;
-            for (int j = 0; j < P.nr; ++j, ++xi) {
+            const bool hi16 = (lane & 16) != 0, hi8 = (lane & 8) != 0;
+            const int jrow = (hi16 ? 2 : 0) + (hi8 ? 1 : 0);
+            // this lane's 32 quantised activations (f16 pairs) and block scale of the next route
+            auto take_route = [&](int j, uint32_t (&xh)[16], float &sa, int &tok) {
                 const int xs = xi % kMoeXSlots;
-                const int route = sorted_s[P.first + j];
-                const int tok = route / p.top_k;
-                if (tid == 0 && j == 0) WS_MARK2(8 + ps * 4 + 0);
+                tok = sorted_s[P.first + j] / p.top_k;
                 mbar_wait(xfull0 + xs * 8, ((uint32_t)(xi / kMoeXSlots)) & 1u, X.status);
-                if (tid == 0 && j == 0) WS_MARK2(8 + ps * 4 + 1);
-                // this lane's 32 quantised activations (f16 pairs) and their block scale
-                uint32_t xh[16];
                 const uint32_t xa = xring0 + xs * S.xbytes;
-                const float sa = lvalid ? lds_f32(xa + p.k * 2 + cs * 4) : 0.0f;
+                sa = lvalid ? lds_f32(xa + p.k * 2 + cs * 4) : 0.0f;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const uint4 v = lds_u128(xa + cs * 64 + q * 16);
@@ -380,41 +402,57 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(xempty0 + xs * 8);  // the values are in registers
+                ++xi;
+            };
+            // rows of this warp, four at a time, against one route or two routes of the expert
+            auto rows_pass = [&](auto rt_c, const uint32_t (&xa)[16], const uint32_t (&xb)[16], float sa, float sb2, int ta,
+                                 int tb) {
+                constexpr int RT = decltype(rt_c)::value;
+                float *acc_a = acc_base + ((size_t)kslice * p.m + ta) * acc_stride + r0;
+                float *acc_b = acc_base + ((size_t)kslice * p.m + tb) * acc_stride + r0;
+                for (int rb = rg; rb < rows; rb += 4 * ng) {
+                    float va[4], vb[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int r = rb + j * ng;
+                        va[j] = vb[j] = 0.0f;
+                        if (r < rows) {  // warp-uniform
+                            const uint4 w = lds_u128(sbase + lane_col + r * 128 + ((uint32_t)(cc ^ (r & 7)) << 4));
+                            const float sw = e8m0_f32(lds_u8(sbase + p.scale_off + r * kb32 + cs));
+                            float da, db;
+                            dot32_e2m1<RT>(w, xa, xb, da, db);
+                            va[j] = da * (sa * sw);
+                            if (RT == 2) vb[j] = db * (sb2 * sw);
+                        }
+                    }
+                    const int r = rb + jrow * ng;
+                    const float ka = fold4(va, hi16, hi8);
+                    if ((lane & 7) == 0 && r < rows) atomicAdd(acc_a + r, ka);  // only this warp ever adds to this address
+                    if (RT == 2) {
+                        const float kb2 = fold4(vb, hi16, hi8);
+                        if ((lane & 7) == 0 && r < rows) atomicAdd(acc_b + r, kb2);
+                    }
+                }
+            };
+            if (tid == 0) WS_MARK2(8 + ps * 4 + 0);
+            for (int j = 0; j < P.nr;) {
+                const int rt = P.nr - j >= 2 ? 2 : 1;
+                uint32_t xa[16], xb[16];
+                float sa, sb2 = 0.0f;
+                int ta, tb = 0;
+                take_route(j, xa, sa, ta);
+                if (rt == 2) take_route(j + 1, xb, sb2, tb);
                 if (!landed) {
+                    if (tid == 0) WS_MARK2(8 + ps * 4 + 1);
                     mbar_wait(full0 + s * 8, ((uint32_t)(item / NS)) & 1u, X.status);
                     landed = true;
                     if (tid == 0) WS_MARK2(8 + ps * 4 + 2);
                 }
                 if (wactive) {
-                    float *acc = acc_base + ((size_t)kslice * p.m + tok) * acc_stride + r0;
-                    // four rows at a time: their 32-lane sums are folded together (4 -> 2 -> 1
-                    // values per lane, then three plain steps), 6 shuffles instead of 20
-                    const bool hi16 = (lane & 16) != 0, hi8 = (lane & 8) != 0;
-                    const int jrow = (hi16 ? 2 : 0) + (hi8 ? 1 : 0);
-                    for (int rb = rg; rb < rows; rb += 4 * ng) {
-                        float v[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int r = rb + j * ng;
-                            v[j] = 0.0f;
-                            if (r < rows) {  // warp-uniform
-                                const uint4 w = lds_u128(sbase + lane_col + r * 128 + ((uint32_t)(cc ^ (r & 7)) << 4));
-                                const uint32_t sb = lds_u8(sbase + p.scale_off + r * kb32 + cs);
-                                v[j] = dot32_e2m1(w, xh) * (sa * e8m0_f32(sb));
-                            }
-                        }
-                        float k0 = hi16 ? v[2] : v[0], k1 = hi16 ? v[3] : v[1];
-                        k0 += __shfl_xor_sync(0xffffffffu, hi16 ? v[0] : v[2], 16);
-                        k1 += __shfl_xor_sync(0xffffffffu, hi16 ? v[1] : v[3], 16);
-                        float k = hi8 ? k1 : k0;
-                        k += __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k1, 8);
-                        k += __shfl_xor_sync(0xffffffffu, k, 4);
-                        k += __shfl_xor_sync(0xffffffffu, k, 2);
-                        k += __shfl_xor_sync(0xffffffffu, k, 1);
-                        const int r = rb + jrow * ng;
-                        if ((lane & 7) == 0 && r < rows) atomicAdd(acc + r, k);  // only this warp ever adds to this address
-                    }
+                    if (rt == 2) rows_pass(std::integral_constant<int, 2>{}, xa, xb, sa, sb2, ta, tb);
+                    else         rows_pass(std::integral_constant<int, 1>{}, xa, xa, sa, sa, ta, ta);
                 }
+                j += rt;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + s * 8);
