@@ -163,6 +163,35 @@ def test_oproj_full_size_tp1(dev, tpmod, oracle):
 
 
 # ----------------------------------------------------------------------------- FP8 GEMM, TP>1
+def test_fp8_host_buffer_call_matches_device_call(dev, tpmod, oracle):
+    """The host-buffer form (the Collectives-style call the reference engine makes,
+    crates/weightstream-gpu/src/engine.rs:287-294: host slice in, owned vector out) gives the bits of
+    the device-resident call.  It replays one cached graph per argument set: repeated calls with new
+    activations, a change of row count, and more weights than the cache holds are all covered."""
+    from weightstream_b200 import formats as F, synth
+    rng = np.random.default_rng(515)
+    n, k = 512, 1024
+    ep = tpmod.Endpoint(max_m=16, max_n=n)
+    try:
+        weights = []
+        for i in range(18):  # the cache keeps 16
+            w, sc = synth.fp8_weight(rng, n, k)
+            weights.append((w, sc, u8(w, dev), torch.from_numpy(sc).to(dev)))
+        for rnd in range(2):
+            for i, (w, sc, wd, sd) in enumerate(weights):
+                m = 1 if (i + rnd) % 3 else 3
+                xb = synth.activations_bf16(rng, m, k)
+                got = ep.fp8_rowpar_gemm_allreduce_host(xb, wd, sd)
+                ref = ep.fp8_rowpar_gemm_allreduce(bf16_tensor(xb, dev), wd, sd)
+                ep.check()
+                assert np.array_equal(got.view(np.uint32), ref.cpu().numpy().view(np.uint32)), (rnd, i)
+                if i < 2:
+                    want = oracle.fp8_gemv(w, sc, F.bf16_bits_to_f32(xb), bn=128, bk=128, threads=oracle.max_threads())
+                    assert rel_l2(got, want) < 5e-5
+    finally:
+        ep.close()
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("n,k,m", [(512, 2048, 1), (7168, 8192, 1), (7168, 8192, 5), (1024, 1024, 19)])
 @pytest.mark.parametrize("kernel", [0, 2, 1])

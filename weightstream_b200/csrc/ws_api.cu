@@ -44,6 +44,17 @@ struct ws_tp {
     size_t pin_bytes = 0;
     void *dev_stage = nullptr;
     size_t dev_stage_bytes = 0;
+    // host-buffer FP8 step replayed as one CUDA graph (copy in, kernel(s), copy out, status out)
+    struct HostGraph {
+        ws_fp8_gemm_args_t key{};
+        void *pin = nullptr, *dev = nullptr;
+        int kernel_sel = 0, split = 0, pdl = 0;
+        uint64_t steps = 0, launches = 0, used = 0;
+        cudaGraphExec_t exec = nullptr;
+    };
+    std::vector<HostGraph> hgraphs;
+    uint32_t *pin_status = nullptr;
+    uint64_t hgraph_clock = 0;
     // MoE decode step: routes quantised once per step, pass table, large-m accumulators
     uint8_t *moe_work = nullptr;
     size_t moe_work_bytes = 0;
@@ -250,6 +261,9 @@ ws_status_t ws_tp_destroy(ws_tp_t *tp) {
     if (tp->hstream) cudaStreamDestroy(tp->hstream);
     if (tp->pin) cudaFreeHost(tp->pin);
     if (tp->dev_stage) cudaFree(tp->dev_stage);
+    for (auto &g : tp->hgraphs)
+        if (g.exec) cudaGraphExecDestroy(g.exec);
+    if (tp->pin_status) cudaFreeHost(tp->pin_status);
     if (tp->moe_work) cudaFree(tp->moe_work);
     if (tp->moe_acc) cudaFree(tp->moe_acc);
     if (tp->sym) cudaFree(tp->sym);
@@ -925,24 +939,84 @@ static ws_status_t coll_host(ws_tp *tp, const float *in, float *out, int64_t len
 ws_status_t ws_allreduce_f32_host(ws_tp_t *tp, const float *in, float *out, int64_t len) { return coll_host(tp, in, out, len, 0); }
 ws_status_t ws_allgather_f32_host(ws_tp_t *tp, const float *in, float *out, int64_t len) { return coll_host(tp, in, out, len, 1); }
 
+// The host-buffer step is the same sequence every time a caller repeats it on one weight (copy
+// the activations in, launch, copy the rows and the status word out), so it is captured once per
+// distinct argument set and replayed as one graph launch; a handful of sets are kept.
+static bool same_fp8_args(const ws_fp8_gemm_args_t &a, const ws_fp8_gemm_args_t &b) {
+    return a.m == b.m && a.n == b.n && a.k == b.k && a.x_dtype == b.x_dtype && a.w == b.w && a.ldw == b.ldw &&
+           a.scales == b.scales && a.scale_ld == b.scale_ld && a.scale_kind == b.scale_kind && a.block_n == b.block_n &&
+           a.block_k == b.block_k && a.row0 == b.row0 && a.k0 == b.k0;
+}
+
 ws_status_t ws_fp8_rowpar_gemm_allreduce_host(ws_tp_t *tp, const ws_fp8_gemm_args_t *dw, const void *x_host, float *out_host) {
     if (!tp || !dw || !x_host || !out_host) return WS_ERR_INVALID;
     const size_t es = dw->x_dtype == WS_ACT_BF16 ? 2 : 4;
     const size_t xb = (size_t)dw->m * dw->k * es, xb_al = (xb + 255) / 256 * 256, ob = (size_t)dw->m * dw->n * 4;
     ws_status_t s = ensure_staging(tp, xb_al + ob, xb_al + ob);
     if (s != WS_OK) return s;
+    if (!tp->pin_status) WS_CUDA(tp, cudaHostAlloc(reinterpret_cast<void **>(&tp->pin_status), 64, cudaHostAllocDefault));
     char *pin = static_cast<char *>(tp->pin), *dev = static_cast<char *>(tp->dev_stage);
-    memcpy(pin, x_host, xb);
-    WS_CUDA(tp, cudaMemcpyAsync(dev, pin, xb, cudaMemcpyHostToDevice, tp->hstream));
     ws_fp8_gemm_args_t a = *dw;
     a.x = dev;
     a.ldx = dw->k;
     a.out = reinterpret_cast<float *>(dev + xb_al);
-    s = ws_fp8_rowpar_gemm_allreduce(tp, &a, tp->hstream);
-    if (s != WS_OK) return s;
-    WS_CUDA(tp, cudaMemcpyAsync(pin + xb_al, dev + xb_al, ob, cudaMemcpyDeviceToHost, tp->hstream));
-    s = ws_tp_check(tp, tp->hstream);
-    if (s != WS_OK) return s;
+
+    ws_tp::HostGraph *hit = nullptr;
+    for (auto &g : tp->hgraphs)
+        if (g.exec && g.pin == pin && g.dev == dev && g.kernel_sel == tp->kernel_sel && g.split == tp->split &&
+            g.pdl == tp->pdl && same_fp8_args(g.key, a))
+            hit = &g;
+    if (!hit) {  // capture; any failure falls back to plain enqueueing below
+        const uint64_t step0 = tp->step, launches0 = tp->launches;
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+        bool ok = cudaStreamBeginCapture(tp->hstream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        if (ok) {
+            ok = cudaMemcpyAsync(dev, pin, xb, cudaMemcpyHostToDevice, tp->hstream) == cudaSuccess;
+            ok = ok && ws_fp8_rowpar_gemm_allreduce(tp, &a, tp->hstream) == WS_OK;
+            ok = ok && cudaMemcpyAsync(pin + xb_al, dev + xb_al, ob, cudaMemcpyDeviceToHost, tp->hstream) == cudaSuccess;
+            ok = ok && cudaMemcpyAsync(tp->pin_status, tp->status, sizeof(uint32_t), cudaMemcpyDeviceToHost, tp->hstream) == cudaSuccess;
+            const bool ended = cudaStreamEndCapture(tp->hstream, &graph) == cudaSuccess && graph != nullptr;
+            ok = ok && ended && cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+            if (graph) cudaGraphDestroy(graph);
+        }
+        const uint64_t steps = tp->step - step0, launches = tp->launches - launches0;
+        tp->step = step0;  // nothing ran yet: the replay below (or the fallback) counts the step
+        tp->launches = launches0;
+        cudaGetLastError();
+        if (ok && exec) {
+            ws_tp::HostGraph *slot = nullptr;
+            if (tp->hgraphs.size() < 16) {
+                tp->hgraphs.emplace_back();
+                slot = &tp->hgraphs.back();
+            } else {
+                slot = &tp->hgraphs[0];
+                for (auto &g : tp->hgraphs)
+                    if (g.used < slot->used) slot = &g;
+                if (slot->exec) cudaGraphExecDestroy(slot->exec);
+            }
+            slot->key = a; slot->pin = pin; slot->dev = dev;
+            slot->kernel_sel = tp->kernel_sel; slot->split = tp->split; slot->pdl = tp->pdl;
+            slot->steps = steps; slot->launches = launches; slot->exec = exec;
+            hit = slot;
+        }
+    }
+    memcpy(pin, x_host, xb);
+    if (hit) {
+        hit->used = ++tp->hgraph_clock;
+        WS_CUDA(tp, cudaGraphLaunch(hit->exec, tp->hstream));
+        tp->step += hit->steps;
+        tp->launches += hit->launches;
+        WS_CUDA(tp, cudaStreamSynchronize(tp->hstream));
+        if (*tp->pin_status != 0u) return ws_tp_check(tp, tp->hstream);  // turns the device code into status + message
+    } else {
+        WS_CUDA(tp, cudaMemcpyAsync(dev, pin, xb, cudaMemcpyHostToDevice, tp->hstream));
+        s = ws_fp8_rowpar_gemm_allreduce(tp, &a, tp->hstream);
+        if (s != WS_OK) return s;
+        WS_CUDA(tp, cudaMemcpyAsync(pin + xb_al, dev + xb_al, ob, cudaMemcpyDeviceToHost, tp->hstream));
+        s = ws_tp_check(tp, tp->hstream);
+        if (s != WS_OK) return s;
+    }
     memcpy(out_host, pin + xb_al, ob);
     return WS_OK;
 }
