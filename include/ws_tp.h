@@ -200,7 +200,7 @@ ws_status_t ws_tp_set_kernel(ws_tp_t *tp, int32_t which);
  * where an allocation is an error, or a plug-in that has no endpoint (ws_tp_create allocates
  * the exchange region).  This is the single-rank form of ws_fp8_rowpar_gemm_allreduce (same
  * arguments, same kernel, out = the whole sum since there is one rank) whose scratch -- the
- * K-split partial sums, their arrival counters and a status word -- is a fixed array inside
+ * kernel's status word, step counter and arrival counters -- is a fixed array inside
  * the library image (WS_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the
  * process exits).  It calls no cudaMalloc / cudaFree and no allocating library routine.
  *
@@ -213,7 +213,7 @@ ws_status_t ws_tp_set_kernel(ws_tp_t *tp, int32_t which);
  *    calls that overlap on the GPU (different streams, no ordering) race on it. */
 #define WS_STATIC_MAX_M 8
 #define WS_STATIC_MAX_N 1048576
-#define WS_STATIC_SCRATCH_BYTES (160 * 16 * 8 * 16 * 4 + (160 + 8) * 4)
+#define WS_STATIC_SCRATCH_BYTES 1024
 ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *args, int32_t device, void *stream,
                                        char *err, size_t err_len);
 

@@ -29,7 +29,6 @@ struct ws_tp {
     char *peers[WS_MAX_WORLD] = {};      // every rank's region as mapped in this process
     bool opened[WS_MAX_WORLD] = {};      // mapped through an IPC handle (must be closed)
     bool connected = false;
-    float *contrib = nullptr;
     uint32_t *counters = nullptr;
     uint32_t *status = nullptr;
     uint64_t step = 0, launches = 0;
@@ -132,7 +131,6 @@ int ragged_granularity(int n, int ncta) {
 RankCtx make_ctx(const ws_tp *tp) {
     RankCtx c{};
     for (int i = 0; i < WS_MAX_WORLD; ++i) c.sym[i] = tp->peers[i];
-    c.contrib = tp->contrib;
     c.counters = tp->counters;
     c.status = tp->status;
     c.step_ctr = tp->counters + kMaxShared + 2;
@@ -236,8 +234,6 @@ ws_status_t ws_tp_create(int32_t world, int32_t rank, int32_t device, const ws_t
     tp->lay = make_layout(world, cfg->max_m, cfg->max_n, cfg->max_vocab);
     if (cudaMalloc(&tp->sym, (size_t)tp->lay.total) != cudaSuccess) return bail(WS_ERR_CUDA);
     if (cudaMemset(tp->sym, 0, (size_t)tp->lay.total) != cudaSuccess) return bail(WS_ERR_CUDA);
-    const size_t contrib_bytes = (size_t)kMaxCtas * kMaxRuns * 8 * kGroupRows * sizeof(float);
-    if (cudaMalloc(&tp->contrib, contrib_bytes) != cudaSuccess) return bail(WS_ERR_CUDA);
     if (cudaMalloc(&tp->counters, (kMaxShared + 8) * sizeof(uint32_t)) != cudaSuccess) return bail(WS_ERR_CUDA);
     if (cudaMemset(tp->counters, 0, (kMaxShared + 8) * sizeof(uint32_t)) != cudaSuccess) return bail(WS_ERR_CUDA);
     tp->status = tp->counters + kMaxShared;
@@ -267,7 +263,6 @@ ws_status_t ws_tp_destroy(ws_tp_t *tp) {
     if (tp->moe_work) cudaFree(tp->moe_work);
     if (tp->moe_acc) cudaFree(tp->moe_acc);
     if (tp->sym) cudaFree(tp->sym);
-    if (tp->contrib) cudaFree(tp->contrib);
     if (tp->counters) cudaFree(tp->counters);
     delete tp;
     return WS_OK;
@@ -345,7 +340,6 @@ ws_status_t ws_tp_check(ws_tp_t *tp, void *stream) {
     WS_CUDA(tp, cudaMemset(tp->status, 0, 4));
     const uint32_t where = st >> 24;
     const char *what = where == 1   ? "a peer CTA's partial"
-                       : where == 2 ? "a peer's split-group partial"
                        : where == 3 ? "a weight tile (TMA)"
                        : where == 4 ? "the gather of every rank"
                                     : "an unknown event";
@@ -1051,12 +1045,11 @@ ws_status_t ws_tp_set_split(ws_tp_t *tp, int32_t on) {
 
 
 // ------------------------------------------------------------------------------ no allocation
-// Scratch for ws_fp8_gemm_static_scratch: the K-split contributions of every CTA, the
-// arrival counters of the split row groups and one status word.  It lives in the library
+// Scratch for ws_fp8_gemm_static_scratch: what the kernel keeps in device memory outside its
+// operands (arrival counters, the status word, the step counter).  It lives in the library
 // image, so every GPU that loads the library holds these bytes until the process exits.
-constexpr size_t kStaticContribFloats = (size_t)kMaxCtas * kMaxRuns * 8 * kGroupRows;
-constexpr size_t kStaticScratchBytes = kStaticContribFloats * sizeof(float) + (kMaxShared + 8) * sizeof(uint32_t);
-static_assert(kStaticScratchBytes == WS_STATIC_SCRATCH_BYTES, "header and library disagree on the scratch size");
+constexpr size_t kStaticScratchBytes = WS_STATIC_SCRATCH_BYTES;
+static_assert((kMaxShared + 8) * sizeof(uint32_t) <= kStaticScratchBytes, "the static scratch is too small for the kernel's counters");
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 namespace {
@@ -1113,9 +1106,8 @@ ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *a, int32_t devi
     unsigned char *base = g_static_scratch_addr[device];
     const int ncta = std::min(g_static_sm_count[device], (int)kMaxCtas);
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    // counters and the status word must start at zero; the contributions are always written
-    // before they are read, so what the previous call left there does not matter
-    ce = cudaMemsetAsync(base + kStaticContribFloats * sizeof(float), 0, (kMaxShared + 8) * sizeof(uint32_t), cs);
+    // counters, status word and step counter must start at zero
+    ce = cudaMemsetAsync(base, 0, (kMaxShared + 8) * sizeof(uint32_t), cs);
     if (ce != cudaSuccess) { set_err(err, err_len, "cudaMemsetAsync: %s", cudaGetErrorString(ce)); return WS_ERR_CUDA; }
 
     Fp8Params p{};
@@ -1145,8 +1137,7 @@ ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *a, int32_t devi
     }
     r.x = a->x; r.scales = a->scales; r.out = a->out;
     r.ldx = a->ldx; r.scale_ld = a->scale_ld; r.row0 = a->row0; r.k0 = a->k0;
-    r.ctx.contrib = reinterpret_cast<float *>(base);
-    r.ctx.counters = reinterpret_cast<uint32_t *>(base + kStaticContribFloats * sizeof(float));
+    r.ctx.counters = reinterpret_cast<uint32_t *>(base);
     r.ctx.status = r.ctx.counters + kMaxShared;
     r.ctx.step_ctr = r.ctx.counters + kMaxShared + 2;
     r.ctx.rank = 0;

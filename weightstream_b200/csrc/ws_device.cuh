@@ -22,15 +22,13 @@ constexpr int kBoxesPerStage = WS_BOXES_PER_STAGE;
 constexpr int kStageBytes = kBoxBytes * kBoxesPerStage;  // 32 KB
 constexpr int kMaxStages = 16;
 constexpr int kMaxCtas = 160;    // persistent CTAs per rank (one per SM on B200: 148)
-constexpr int kMaxShared = 160;  // output row groups whose K range is split across CTAs
-constexpr int kMaxRuns = 16;     // split contributions one CTA may produce
+constexpr int kMaxShared = 160;  // further counter / flag slots per rank (status word and step counter follow them)
 constexpr int kGroupRows = 16;   // MMA M: output rows per group
 
 // Error detail codes written to the device status word (high byte) with WS_ERR_*.
 enum : uint32_t {
     kStatOk = 0,
     kStatTimeoutPeerA = 0x01000000u,  // waiting for a peer CTA's owned-rows flag
-    kStatTimeoutPeerB = 0x02000000u,  // waiting for a peer's split-group flag
     kStatTimeoutTma = 0x03000000u,    // a weight tile never landed in shared memory
     kStatTimeoutGather = 0x04000000u
 };
@@ -40,7 +38,7 @@ enum : uint32_t {
 struct SymLayout {
     int64_t flags_off;   // u32  [2 banks][R src][kMaxCtas + kMaxShared]
     int64_t pairs_off;   // u64  [2][R][kMaxCtas][max_m]      (argmax candidates)
-    int64_t slotb_off;   // f32  [2][R][kMaxShared][8*16... sized max_m*16]
+    int64_t slotf_off;   // f32  [2][R][max_m*max_n]  plain-float slots (flag-synchronised exchanges: gather, MMA-form MoE, tcgen05 kernel)
     int64_t slota_off;   // u64  [2][R][max_m*max_n]  {step sequence, fp32 bits} words of the all-reduce
     int64_t gather_off;  // f32  [2][max_m*max_vocab]
     int64_t total;
@@ -55,7 +53,7 @@ __host__ inline SymLayout make_layout(int world, int max_m, int max_n, int max_v
     int64_t o = 0;
     L.flags_off = o;  o += align_up((int64_t)2 * world * (kMaxCtas + kMaxShared) * 4, 256);
     L.pairs_off = o;  o += align_up((int64_t)2 * world * kMaxCtas * max_m * 8, 256);
-    L.slotb_off = o;  o += align_up((int64_t)2 * world * kMaxShared * max_m * kGroupRows * 4, 256);
+    L.slotf_off = o;  o += align_up((int64_t)2 * world * max_m * max_n * 4, 256);
     L.slota_off = o;  o += align_up((int64_t)2 * world * max_m * max_n * 8, 256);
     L.gather_off = o; o += align_up((int64_t)2 * max_m * (int64_t)max_vocab * 4, 256);
     L.total = o;
@@ -65,7 +63,6 @@ __host__ inline SymLayout make_layout(int world, int max_m, int max_n, int max_v
 // What one (possibly virtual) rank needs inside a kernel to reach its group.
 struct RankCtx {
     char *sym[WS_MAX_WORLD];  // sym[p] = rank p's exchange region as mapped here
-    float *contrib;           // local: [kMaxCtas][kMaxRuns][8*16] split contributions
     uint32_t *counters;       // local: [kMaxShared] arrival counters (self-resetting)
     uint32_t *status;         // local: first error wins
     uint32_t *step_ctr;       // local: [0] steps completed by this rank, [1] CTAs done with the current step
@@ -132,19 +129,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
-__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1,
                                             uint32_t &r2, uint32_t &r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t &r0, uint32_t &r1) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
-                 : "=r"(r0), "=r"(r1)
                  : "r"(addr));
 }
 
@@ -254,11 +243,6 @@ __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ float ld_volatile_f32(const float *p) {
-    float v;
-    asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ uint64_t ld_volatile_u64(const uint64_t *p) {

@@ -124,15 +124,6 @@ __host__ __device__ inline RowPlan row_plan(int n, int ncta, int cta, int ragged
     return r;
 }
 
-// Split schedule helpers used by the MoE kernel (K-split leftover tiles).
-// All products stay below 2^32 (U <= 160*512*64 units, ncta <= 160), so 32-bit division does.
-__host__ __device__ __forceinline__ int64_t unit_begin(int c, int64_t U, int ncta) {
-    return (int64_t)((uint32_t)c * (uint32_t)U / (uint32_t)ncta);
-}
-__host__ __device__ __forceinline__ int owner_of(int64_t u, int64_t U, int ncta) {
-    return (int)((((uint32_t)u + 1u) * (uint32_t)ncta + (uint32_t)U - 1u) / (uint32_t)U) - 1;
-}
-
 __device__ __forceinline__ bool cand_better(float v, uint32_t i, float bv, uint32_t bi) {
     return v > bv || (v == bv && i < bi);
 }

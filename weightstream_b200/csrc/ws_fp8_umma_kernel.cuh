@@ -373,7 +373,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
                             if (t < p.m) A.out[(size_t)t * p.n + row] = acc[t];
                     } else if (p.mode == kModeAllReduce) {
                         for (int pr = 0; pr < p.world; ++pr) {
-                            float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slota_off) +
+                            float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slotf_off) +
                                          ((size_t)bank * p.world + X.rank) * astride;
 #pragma unroll
                             for (int t = 0; t < 8; ++t)
@@ -410,7 +410,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
                     wait_flag(myflags + (size_t)et * nflag + cta, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
                 }
                 epi_bar();
-                const float *slots = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.slota_off) +
+                const float *slots = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.slotf_off) +
                                      (size_t)bank * p.world * astride;
                 for (int c = 0; c < p.nchunk; ++c) {
                     const int row = row_a + c * p.chunk_rows + rc;

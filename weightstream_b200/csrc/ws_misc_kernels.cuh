@@ -49,7 +49,7 @@ __device__ __forceinline__ void coll_body(const CollParams &p, const uint32_t se
     // all-gather: plain stores into the (float-addressed) slots, one released flag per CTA and peer
     const int nflag = kMaxCtas + kMaxShared;
     for (int pr = 0; pr < p.world; ++pr) {
-        float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
+        float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slotf_off) + ((size_t)bank * p.world + X.rank) * astride;
         for (int64_t i = a + tid; i < b; i += blockDim.x) dst[i] = A.in[i];
     }
     __syncthreads();  // the st.release.sys below is cumulative over the stores this barrier ordered
@@ -60,7 +60,7 @@ __device__ __forceinline__ void coll_body(const CollParams &p, const uint32_t se
     const uint32_t *myflags = reinterpret_cast<const uint32_t *>(X.sym[X.rank] + p.lay.flags_off) + (size_t)bank * p.world * nflag;
     if (tid < p.world) wait_flag(myflags + (size_t)tid * nflag + cta, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
     __syncthreads();
-    const float *slots = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.slota_off) + (size_t)bank * p.world * astride;
+    const float *slots = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.slotf_off) + (size_t)bank * p.world * astride;
     for (int r = 0; r < p.world; ++r)
         for (int64_t i = a + tid; i < b; i += blockDim.x) A.out[(int64_t)r * p.len + i] = __ldcg(slots + r * astride + i);
 }

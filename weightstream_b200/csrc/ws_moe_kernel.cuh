@@ -113,7 +113,6 @@ __device__ __forceinline__ void moe_down_body(const MoeParams &p) {
     const int ntile = R.Gm + nx;
     auto trow = [&](int t) { return t < R.Gm ? (cta * R.Gm + t) * kGroupRows : (t == R.Gm ? xa : xmid); };
     auto tcnt = [&](int t) { return t < R.Gm ? kGroupRows : (t == R.Gm ? xmid - xa : xb - xmid); };
-    const int nitem_pass = (ntile + TPI - 1) / TPI;  // stage items per pass
     const int PR = p.part_rows;
 
     const MoeSmem S = moe_smem_layout(p.nstages, TPI, p.k, p.m, p.top_k, A.e_len, PR);
@@ -396,7 +395,7 @@ __device__ __forceinline__ void moe_down_body(const MoeParams &p) {
     }
     const size_t astride = (size_t)p.lay.max_m * p.lay.max_n;
     for (int pr = 0; pr < p.world; ++pr) {
-        float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
+        float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.slotf_off) + ((size_t)bank * p.world + X.rank) * astride;
         for_rows([&](int tok, int row, int pi) { dst[(size_t)tok * p.n + row] = part_s[pi]; });
     }
     consumer_bar();  // the st.release.sys below is cumulative over the stores this barrier ordered
@@ -408,7 +407,7 @@ __device__ __forceinline__ void moe_down_body(const MoeParams &p) {
         wait_flag(myflags + (size_t)tid * nflag + cta, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
     }
     consumer_bar();
-    const float *slots = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.slota_off) + (size_t)bank * p.world * astride;
+    const float *slots = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.slotf_off) + (size_t)bank * p.world * astride;
     for_rows([&](int tok, int row, int) {
         const size_t off = (size_t)tok * p.n + row;
         float s = __ldcg(slots + off);
