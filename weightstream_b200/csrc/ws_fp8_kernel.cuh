@@ -422,7 +422,6 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         const uint32_t sbase = stage0 + s * kStageBytes;
         const uint32_t swrow = smem_u32(sw_s) + (uint32_t)(slot * p.skb * 4);
         const uint32_t xbase = smem_u32(q_s) + (uint32_t)(cch * 32);
-#ifndef WS_PROBE_NOCOMPUTE
         for (int bi = warp; bi < nb; bi += CW) {
             const int box = b0 + bi;
             const int kb = box * 4 + (cch >> 1);  // the 32-wide K block of this lane's chunk
@@ -455,7 +454,6 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
                 }
             }
         }
-#endif
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + s * 8);
         ++item;
