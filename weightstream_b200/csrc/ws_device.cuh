@@ -94,8 +94,12 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+#ifndef WS_WAIT_MODE
+#define WS_WAIT_MODE 0
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
+#if WS_WAIT_MODE == 0
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
@@ -103,6 +107,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok)
         : "r"(bar), "r"(parity), "r"(20000u)  // the thread may sleep until the phase completes (at most ~20 us per probe)
         : "memory");
+#elif WS_WAIT_MODE == 1
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+#else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+#endif
     return ok != 0;
 }
 // Bounded wait: gives up after two seconds of wall time (globaltimer), records why, and lets the
@@ -119,6 +136,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
     atomicCAS(status, 0u, kStatTimeoutTma | (uint32_t)(-WS_ERR_TIMEOUT));
     return false;
 }
+
+// Position in a ring of `n` stages, advanced without the division and remainder that
+// (item % n, item / n) would cost per stage and warp.
+struct RingPos {
+    int s = 0;        // stage
+    uint32_t ph = 0;  // parity of the number of completed laps
+    __device__ __forceinline__ void next(int n) {
+        if (++s == n) {
+            s = 0;
+            ph ^= 1u;
+        }
+    }
+};
 
 // 2-D TMA tile load global -> shared, completion on an mbarrier (no multicast).
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int32_t x,

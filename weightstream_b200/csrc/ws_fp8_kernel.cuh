@@ -181,15 +181,14 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
 
     if (warp == CW) {
         // ------------------------------------------------------------ TMA producer warp
-        int item = 0;
+        RingPos rp;
         for (int t = 0; t < ntile; ++t) {
             const int r0 = trow(t), cnt = tcnt(t);
             const int pad = tpad(cnt), cols = kStageBytes / (pad * 128);  // box columns one stage holds
             for (int b0 = 0; b0 < kbox; b0 += cols) {
                 const int nb = min(cols, kbox - b0);
-                const int s = item % NS;
-                const uint32_t ph = (uint32_t)(item / NS) & 1u;
-                mbar_wait(empty0 + s * 8, ph ^ 1u, X.status);
+                const int s = rp.s;
+                mbar_wait(empty0 + s * 8, rp.ph ^ 1u, X.status);
                 if (lane == 0) mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)(nb * cnt * 128));
                 __syncwarp();
                 for (int col = lane; col < nb; col += 32) {
@@ -201,7 +200,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
                             tma_load_2d(dst + done * 128, &p.tmap[vr][1], (b0 + col) * 128, r0 + done, full0 + s * 8);
                     }
                 }
-                ++item;
+                rp.next(NS);
             }
         }
         return;
@@ -261,7 +260,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int c = c0 + u * CT;
-                tok[u] = c / chunks_per_row;
+                tok[u] = p.mp == 1 ? 0 : c / chunks_per_row;
                 ch[u] = c - tok[u] * chunks_per_row;
                 valid[u] = (c < total) && (tok[u] < p.m) && (ch[u] * 8 < p.k);
                 load_act8(A.x, p.x_dtype, (int64_t)tok[u] * A.ldx + ch[u] * 8, valid[u], v[u]);
@@ -307,6 +306,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     const int lm_hi = lane >> 4;                            // 0: k 0..15 of the block, 1: k 16..31
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     int item = 0;
+    RingPos rp;
     int redbuf = 0;
 
     const int kofs = (int)(A.k0 - kcol0 * p.bk);  // k0 modulo the scale block
@@ -339,8 +339,8 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         acc[3] = fmaf(d[3], f1, acc[3]);
     };
     auto run_item = [&](int b0, int nb, int slot, int pad) {
-        const int s = item % NS;
-        mbar_wait(full0 + s * 8, (uint32_t)(item / NS) & 1u, X.status);
+        const int s = rp.s;
+        mbar_wait(full0 + s * 8, rp.ph, X.status);
         if (item == 0) WS_MARK(4);
         const uint32_t sbase = stage0 + s * kStageBytes;
         const uint32_t swrow = smem_u32(sw_s) + (uint32_t)(slot * p.skb * 4);
@@ -366,6 +366,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + s * 8);
         ++item;
+        rp.next(NS);
     };
     // Sum the consumer warps' accumulators in warp order; thread t < 128 ends with
     // the value of (row = t & 15, tok = t >> 4).
@@ -416,8 +417,8 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         }
     };
     auto run_item_gemv = [&](int b0, int nb, int slot, int pad) {
-        const int s = item % NS;
-        mbar_wait(full0 + s * 8, (uint32_t)(item / NS) & 1u, X.status);
+        const int s = rp.s;
+        mbar_wait(full0 + s * 8, rp.ph, X.status);
         if (item == 0) WS_MARK(4);
         const uint32_t sbase = stage0 + s * kStageBytes;
         const uint32_t swrow = smem_u32(sw_s) + (uint32_t)(slot * p.skb * 4);
@@ -457,6 +458,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + s * 8);
         ++item;
+        rp.next(NS);
     };
     // Combine the eight lanes of each row, then the warps in warp order (same result layout as
     // reduce_warps: thread t < 128 ends with row t & 15 of token t >> 4).

@@ -52,7 +52,7 @@ struct MoePass {
 
 // Per-endpoint scratch written by moe_prep_kernel and read by moe_gemv_kernel.
 struct MoeWork {
-    int64_t hdr, pass, sorted, sa, xq, total;  // byte offsets
+    int64_t hdr, pass, sorted, stok, sa, xq, total;  // byte offsets
 };
 __host__ __device__ inline MoeWork moe_work_layout(int k) {
     MoeWork w{};
@@ -60,6 +60,7 @@ __host__ __device__ inline MoeWork moe_work_layout(int k) {
     w.hdr = o;    o += 64;
     w.pass = o;   o += (int64_t)kMoeMaxRoutes * sizeof(MoePass);
     w.sorted = o; o += align_up((int64_t)kMoeMaxRoutes * 2, 64);
+    w.stok = o;   o += align_up((int64_t)kMoeMaxRoutes * 2, 64);
     w.sa = o;     o += (int64_t)kMoeMaxRoutes * (k / 32) * 4;
     w.xq = o;     o += (int64_t)kMoeMaxRoutes * k * 2;
     w.total = o;
@@ -150,12 +151,17 @@ __global__ void __launch_bounds__(256) moe_prep_kernel(const __grid_constant__ M
     __syncthreads();
     MoePass *pass = reinterpret_cast<MoePass *>(A.work + W.pass);
     uint16_t *sorted = reinterpret_cast<uint16_t *>(A.work + W.sorted);
+    uint16_t *stok = reinterpret_cast<uint16_t *>(A.work + W.stok);  // the routes' tokens, same order
     for (int e = tid; e < A.e_len; e += blockDim.x) {
         const int c = cnt_s[e];
         if (c == 0) continue;
         int idx = rstart_s[e];
         for (int r = 0; r < NR; ++r)
-            if (ids_s[r] == e) sorted[idx++] = (uint16_t)r;
+            if (ids_s[r] == e) {
+                sorted[idx] = (uint16_t)r;
+                stok[idx] = (uint16_t)(r / p.top_k);
+                ++idx;
+            }
         for (int q = 0; q * kMoeRoutesPerPass < c; ++q) {
             MoePass ps;
             ps.expert = (uint16_t)e;
@@ -189,7 +195,7 @@ struct alignas(64) MoeGemvParams {
 };
 
 struct MoeGemvSmem {
-    int32_t stages, xring, acc, pass, sorted, bars, total;
+    int32_t stages, xring, acc, pass, sorted, stok, bars, total;
     int32_t xbytes;
 };
 __host__ __device__ inline int moe_gemv_slices(int k) { return (k / 32 + 31) / 32; }  // warps along K
@@ -203,6 +209,7 @@ __host__ __device__ inline MoeGemvSmem moe_gemv_smem(int nstages, int stage_byte
     s.acc = o;    o += acc_global ? 0 : (int)align_up((int64_t)moe_gemv_slices(k) * m * acc_rows * 4, 16);
     s.pass = o;   o += kMoeMaxRoutes * (int)sizeof(MoePass);
     s.sorted = o; o += kMoeMaxRoutes * 2;
+    s.stok = o;   o += kMoeMaxRoutes * 2;
     s.bars = o;   o += (2 * kMaxStages + 2 * kMoeXSlots) * 8;
     s.total = o;
     return s;
@@ -277,6 +284,7 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
     const MoeWork W = moe_work_layout(p.k);
     MoePass *pass_s = reinterpret_cast<MoePass *>(smem + S.pass);
     uint16_t *sorted_s = reinterpret_cast<uint16_t *>(smem + S.sorted);
+    uint16_t *stok_s = reinterpret_cast<uint16_t *>(smem + S.stok);
     const uint32_t stage0 = smem_u32(smem + S.stages), xring0 = smem_u32(smem + S.xring);
     const uint32_t full0 = smem_u32(smem + S.bars), empty0 = full0 + kMaxStages * 8;
     const uint32_t xfull0 = empty0 + kMaxStages * 8, xempty0 = xfull0 + kMoeXSlots * 8;
@@ -305,7 +313,11 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
         const uint2 *src = reinterpret_cast<const uint2 *>(A.work + W.pass);
         for (int i = tid; i < NP; i += kMoeGemvThreads) reinterpret_cast<uint2 *>(pass_s)[i] = src[i];
         const uint16_t *ss = reinterpret_cast<const uint16_t *>(A.work + W.sorted);
-        for (int i = tid; i < p.m * p.top_k; i += kMoeGemvThreads) sorted_s[i] = ss[i];
+        const uint16_t *st = reinterpret_cast<const uint16_t *>(A.work + W.stok);
+        for (int i = tid; i < p.m * p.top_k; i += kMoeGemvThreads) {
+            sorted_s[i] = ss[i];
+            stok_s[i] = st[i];
+        }
     }
     // zero this CTA's accumulators
     if (p.acc_global) {
@@ -322,11 +334,12 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
 
     if (warp == CW) {
         // ------------------------------------------------------------ producer warp
-        int item = 0, xi = 0;
+        int xi = 0;
+        RingPos rp;
         for (int pn = 0; pn < npanel; ++pn) {
             const int r0 = row_a + pn * p.panel_rows, rows = min(p.panel_rows, row_b - r0);
             const int nb16 = rows >> 4, nbg = (rows & 15) / p.gran, nbox = nb16 + nbg;
-            for (int ps = 0; ps < NP; ++ps, ++item) {
+            for (int ps = 0; ps < NP; ++ps, rp.next(NS)) {
                 const MoePass P = pass_s[ps];
                 for (int j = 0; j < P.nr; ++j, ++xi) {  // the pass's activations, one ring slot per route
                     const int xs = xi % kMoeXSlots;
@@ -344,9 +357,9 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
                     }
                     __syncwarp();
                 }
-                const int s = item % NS;
+                const int s = rp.s;
                 const int64_t erow = (int64_t)P.expert * p.n + r0;
-                mbar_wait(empty0 + s * 8, (((uint32_t)(item / NS)) & 1u) ^ 1u, X.status);
+                mbar_wait(empty0 + s * 8, rp.ph ^ 1u, X.status);
                 const uint32_t sbase = stage0 + s * p.stage_bytes;
                 if (lane == 0) {
                     mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)(rows * (kbytes + kb32)));
@@ -378,12 +391,13 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
     const int cs = lvalid ? c : 0;               // idle lanes read block 0 and multiply by zero
     const uint32_t lane_col = (uint32_t)((cs >> 3) * colpitch);
     const int cc = cs & 7;
-    int item = 0, xi = 0;
+    int xi = 0;
+    RingPos rp;
     for (int pn = 0; pn < npanel; ++pn) {
         const int r0 = pn * p.panel_rows, rows = min(p.panel_rows, rows_cta - r0);  // r0 relative to row_a
-        for (int ps = 0; ps < NP; ++ps, ++item) {
+        for (int ps = 0; ps < NP; ++ps, rp.next(NS)) {
             const MoePass P = pass_s[ps];
-            const int s = item % NS;
+            const int s = rp.s;
             const uint32_t sbase = stage0 + s * p.stage_bytes;
             bool landed = false;
             const bool hi16 = (lane & 16) != 0, hi8 = (lane & 8) != 0;
@@ -391,7 +405,7 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
             // this lane's 32 quantised activations (f16 pairs) and block scale of the next route
             auto take_route = [&](int j, uint32_t (&xh)[16], float &sa, int &tok) {
                 const int xs = xi % kMoeXSlots;
-                tok = sorted_s[P.first + j] / p.top_k;
+                tok = stok_s[P.first + j];
                 mbar_wait(xfull0 + xs * 8, ((uint32_t)(xi / kMoeXSlots)) & 1u, X.status);
                 const uint32_t xa = xring0 + xs * S.xbytes;
                 sa = lvalid ? lds_f32(xa + p.k * 2 + cs * 4) : 0.0f;
@@ -444,7 +458,7 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
                 if (rt == 2) take_route(j + 1, xb, sb2, tb);
                 if (!landed) {
                     if (tid == 0) WS_MARK2(8 + ps * 4 + 1);
-                    mbar_wait(full0 + s * 8, ((uint32_t)(item / NS)) & 1u, X.status);
+                    mbar_wait(full0 + s * 8, rp.ph, X.status);
                     landed = true;
                     if (tid == 0) WS_MARK2(8 + ps * 4 + 2);
                 }
