@@ -466,7 +466,7 @@ static int fp8_rows_per_launch(const ws_tp *t0, const ws_fp8_gemm_args_t &a, int
     for (int mp = std::min(64, (rem + 7) / 8 * 8); mp > 8; mp -= 8) {
         const int m = std::min(rem, mp);
         const Fp8Smem fixed = fp8_smem_layout(0, kbox, mp, (Gm * kGroupRows) / a.block_n + 4, skb, m, (Gm + 2) * kGroupRows, 0);
-        if ((kSmemBudget - fixed.total) / kStageBytes >= 3) return m;
+        if ((kSmemBudget - fixed.total) / (fp8_stage_boxes(kbox) * kBoxBytes) >= 3) return m;
     }
     return 8;
 }
@@ -515,7 +515,8 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
     const int gt = (t0->kernel_sel != 1 && mt <= 2) ? mt : 0;
     void (*const kernel)(Fp8Params) = gt == 1 ? fp8_rowpar_kernel<1> : gt == 2 ? fp8_rowpar_kernel<2> : fp8_rowpar_kernel<0>;
     const Fp8Smem fixed = fp8_smem_layout(0, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows, gt);
-    int ns = (kSmemBudget - fixed.total) / kStageBytes;
+    p.stage_bytes = fp8_stage_boxes(kbox) * kBoxBytes;
+    int ns = (kSmemBudget - fixed.total) / p.stage_bytes;
     if (ns > kMaxStages) ns = kMaxStages;
     if (ns < 2) return fail(t0, WS_ERR_CAPACITY, "shapes m=%d n=%d k=%d leave no room for the weight stage ring", p.m, p.n, p.k);
     p.nstages = ns;
@@ -1125,7 +1126,8 @@ ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *a, int32_t devi
     p.gran = ragged_granularity(p.n, ncta);
     p.part_rows = (Gm + 2) * kGroupRows;
     const Fp8Smem fixed = fp8_smem_layout(0, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows, 0);
-    int ns = std::min((kSmemBudget - fixed.total) / kStageBytes, (int)kMaxStages);
+    p.stage_bytes = fp8_stage_boxes(kbox) * kBoxBytes;
+    int ns = std::min((kSmemBudget - fixed.total) / p.stage_bytes, (int)kMaxStages);
     if (ns < 2) { set_err(err, err_len, "shapes m=%d n=%d k=%d leave no room for the weight stage ring", p.m, p.n, p.k); return WS_ERR_CAPACITY; }
     p.nstages = ns;
     const size_t smem = (size_t)fp8_smem_layout(ns, kbox, p.mp, p.nslot_max, p.skb, p.m, p.part_rows, 0).total + 1024;

@@ -65,6 +65,7 @@ struct alignas(64) Fp8Params {
     int32_t gather_logits, ragged;   // ragged = 0: leftover tiles go whole to the first CTAs
     int32_t bk_shift, bn_shift;      // log2 of the scale block edges
     int32_t part_rows, gran;         // partial rows reserved per token; row granularity (1,2,4,8) of the ragged share
+    int32_t stage_bytes, pad1;       // bytes of one weight stage: a whole number of 2 KB boxes (fp8_stage_boxes)
     uint64_t timeout_ns;
     SymLayout lay;
     Fp8RankArgs r[WS_MAX_WORLD];
@@ -84,11 +85,19 @@ struct Fp8Smem {  // byte offsets from the 1024-aligned base
 
 // gt: 0 for the MMA formulation (activations kept as E4M3 bytes, [kb][tok][32]), else the number
 // of activation rows of the CUDA-core formulation (kept as f16, [tok][kbox*128]).
+// Boxes (16 rows x 128 bytes) per stage: a tile's kbox boxes are cut into equal stages of at most
+// kBoxesPerStage, so that no stage travels half empty (7168 columns = 56 boxes: four stages of 14
+// instead of 16 + 16 + 16 + 8).
+__host__ __device__ inline int fp8_stage_boxes(int kbox) {
+    const int per_tile = (kbox + kBoxesPerStage - 1) / kBoxesPerStage;
+    return (kbox + per_tile - 1) / per_tile;
+}
+
 __host__ __device__ inline Fp8Smem fp8_smem_layout(int nstages, int kbox, int mp, int nslot_max, int skb,
                                                    int m, int part_rows, int gt) {
     Fp8Smem s{};
     int o = 0;
-    s.stages = o; o += nstages * kStageBytes;
+    s.stages = o; o += nstages * fp8_stage_boxes(kbox) * kBoxBytes;
     s.q = o;      o += gt > 0 ? kbox * 128 * 2 * gt : kbox * 4 * mp * 32;
     s.sa = o;     o += kbox * 4 * (mp > 8 ? mp : 8) * 4;
     s.sw = o;     o += ((nslot_max * skb * 4 + 15) / 16) * 16;
@@ -184,7 +193,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         RingPos rp;
         for (int t = 0; t < ntile; ++t) {
             const int r0 = trow(t), cnt = tcnt(t);
-            const int pad = tpad(cnt), cols = kStageBytes / (pad * 128);  // box columns one stage holds
+            const int pad = tpad(cnt), cols = p.stage_bytes / (pad * 128);  // box columns one stage holds
             for (int b0 = 0; b0 < kbox; b0 += cols) {
                 const int nb = min(cols, kbox - b0);
                 const int s = rp.s;
@@ -192,7 +201,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
                 if (lane == 0) mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)(nb * cnt * 128));
                 __syncwarp();
                 for (int col = lane; col < nb; col += 32) {
-                    const uint32_t dst = stage0 + s * kStageBytes + col * pad * 128;
+                    const uint32_t dst = stage0 + s * p.stage_bytes + col * pad * 128;
                     if (cnt == kGroupRows) {  // a whole tile is one 16-row box, a ragged one is cnt/gran small boxes
                         tma_load_2d(dst, &p.tmap[vr][0], (b0 + col) * 128, r0, full0 + s * 8);
                     } else {
@@ -342,7 +351,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         const int s = rp.s;
         mbar_wait(full0 + s * 8, rp.ph, X.status);
         if (item == 0) WS_MARK(4);
-        const uint32_t sbase = stage0 + s * kStageBytes;
+        const uint32_t sbase = stage0 + s * p.stage_bytes;
         const uint32_t swrow = smem_u32(sw_s) + (uint32_t)(slot * p.skb * 4);
         for (int bi = wide ? 0 : warp; bi < nb && tg_active; bi += wide ? 1 : CW) {
             const int box = b0 + bi;
@@ -420,7 +429,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         const int s = rp.s;
         mbar_wait(full0 + s * 8, rp.ph, X.status);
         if (item == 0) WS_MARK(4);
-        const uint32_t sbase = stage0 + s * kStageBytes;
+        const uint32_t sbase = stage0 + s * p.stage_bytes;
         const uint32_t swrow = smem_u32(sw_s) + (uint32_t)(slot * p.skb * 4);
         const uint32_t xbase = smem_u32(q_s) + (uint32_t)(cch * 32);
         for (int bi = warp; bi < nb; bi += CW) {
@@ -492,7 +501,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
 
     for (int t = 0; t < ntile; ++t) {
         const int slot = slot_of(t);
-        const int pad = tpad(tcnt(t)), cols = kStageBytes / (pad * 128);
+        const int pad = tpad(tcnt(t)), cols = p.stage_bytes / (pad * 128);
         float v;
         if constexpr (GT > 0) {
 #pragma unroll
