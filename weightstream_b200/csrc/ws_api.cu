@@ -981,7 +981,7 @@ ws_status_t ws_fp8_rowpar_gemm_allreduce_host(ws_tp_t *tp, const ws_fp8_gemm_arg
         cudaGetLastError();
         if (ok && exec) {
             ws_tp::HostGraph *slot = nullptr;
-            if (tp->hgraphs.size() < 16) {
+            if (tp->hgraphs.size() < 256) {  // one per weight a caller cycles through (a model's layers)
                 tp->hgraphs.emplace_back();
                 slot = &tp->hgraphs.back();
             } else {
