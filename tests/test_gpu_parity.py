@@ -416,6 +416,30 @@ def test_moe_down_combine_tp1(dev, tpmod, oracle, m, n_experts, top_k, n, k, spl
         ep.close()
 
 
+@pytest.mark.parametrize("num_ctas,m,n,k", [
+    (4, 24, 2048, 512),    # 512 rows per CTA: walked in several panels; accumulators in global memory
+    (8, 40, 1024, 512),    # 128 rows per CTA in one panel; accumulators in global memory
+    (3, 2, 1024, 2048),    # uneven row ranges (1024 / 3) in several panels, two K slices, accumulators in shared memory
+])
+def test_moe_decode_form_with_long_row_ranges(dev, tpmod, oracle, num_ctas, m, n, k):
+    """The decode form of the MoE step on few CTAs, so that a CTA's row range no longer fits one
+    stage (panels) and the (K slice, token, row) accumulators no longer fit shared memory."""
+    from weightstream_b200 import formats as F
+    n_experts, top_k = 8, 2
+    rng = np.random.default_rng(4000 + num_ctas + m)
+    w2, s2, ids, rw, hb = moe_case(rng, m, n_experts, top_k, n, k)
+    ep = tpmod.Endpoint(max_m=64, max_n=n, num_ctas=num_ctas)
+    try:
+        out = ep.moe_down_combine_allreduce(bf16_tensor(hb, dev), torch.from_numpy(ids).to(dev),
+                                            torch.from_numpy(rw).to(dev), u8(w2, dev), u8(s2, dev), 0)
+        ep.check()
+        want = oracle.moe_down_combine(w2, s2, 0, F.bf16_bits_to_f32(hb), ids, rw, threads=oracle.max_threads())
+        err = rel_l2(out.cpu().numpy(), want)
+        assert err <= REL_L2_TOL and err < 5e-5, err
+    finally:
+        ep.close()
+
+
 @pytest.mark.parametrize("world", [2, 8])
 @pytest.mark.parametrize("m", [1, 8, 64])
 @pytest.mark.parametrize("kernel", [0, 1])
