@@ -302,7 +302,7 @@ def test_wait_times_out_and_context_survives(dev, tpmod):
 
 # ----------------------------------------------------------------------------- lm_head
 @pytest.mark.parametrize("world", [1, 2, 8])
-@pytest.mark.parametrize("m", [1, 3])
+@pytest.mark.parametrize("m", [1, 2, 3, 20])  # CUDA-core form (1, 2), MMA form (3), all rows in one wide launch (20)
 @pytest.mark.parametrize("kernel", [0, 2, 1])
 def test_lm_head_small_vs_oracle(dev, tpmod, oracle, world, m, kernel):
     """Vocab-sharded head whose shards cut a 128-row scale block (as 129280/8 does): logits equal
@@ -314,7 +314,7 @@ def test_lm_head_small_vs_oracle(dev, tpmod, oracle, world, m, kernel):
     xb = synth.activations_bf16(rng, m, k)
     xf = F.bf16_bits_to_f32(xb)
     want = oracle.fp8_gemv(w, sc, xf, bn=128, bk=128, threads=oracle.max_threads())
-    grp = tpmod.LocalGroup(world, max_m=8, max_n=16, max_vocab=vocab)
+    grp = tpmod.LocalGroup(world, max_m=32, max_n=16, max_vocab=vocab)
     grp.set_kernel(kernel)
     try:
         wd, sd, xd = u8(w, dev), torch.from_numpy(sc).to(dev), bf16_tensor(xb, dev)
