@@ -1,19 +1,28 @@
 #!/usr/bin/env python
-"""Benchmark of the fused tensor-parallel reduction step on B200.
+"""Benchmark of the fused tensor-parallel reduction steps on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload o_proj|shared_down|moe_down|lm_head] [--m M]
 
-One "step" is one fused attention-output-projection step: the row-parallel FP8 GEMM
-(x bf16 [M, 8192/N] against this rank's K slice of W FP8 E4M3 [7168, 8192], 128x128 fp32
-block scales) together with the rank-ordered fp32 all-reduce, M = 1 (decode).  Work is
-fixed and K is split over the N GPUs (strong scaling).  Consecutive steps use different
-weight sets ("layers"), together several times larger than L2, so every step streams its
-weights from HBM.  The line printed on rank 0 carries the device-timed value, the
-end-to-end value through host buffers, the HBM roofline of the kernel, and the CPU
-baseline (the oracle port of the reference's single-threaded CPU path) timed beside it.
+The headline "step" is one fused attention-output-projection step: the row-parallel FP8 GEMM
+(x bf16 [M, 8192/N] against this rank's K slice of W FP8 E4M3 [7168, 8192], 128x128 fp32 block
+scales) together with the rank-ordered fp32 all-reduce, M = 1 (decode).  Work is fixed and K is
+split over the N GPUs (strong scaling).  Consecutive steps use different weight sets ("layers"),
+together several times larger than L2, so every step streams its weights from HBM.
 
-With --impl reference the reference's CPU implementation of the same step (the oracle
-port, all host threads) is timed instead; nothing of the CUDA library is used.
+`value` is the time per step of a chain of K steps replayed as one CUDA graph (consecutive
+kernels overlap through programmatic dependent launch: a step prefetches its weights while its
+predecessor finishes), i.e. the throughput of the decode loop's chain, not the latency of one
+isolated step; `isolated_us` beside it is that latency.  Before anything is timed, one step's
+result is compared with the CPU oracle and across ranks (`parity`); a mismatch ends the run
+with a non-zero exit code.
+
+The line printed on rank 0 also carries the end-to-end value through host buffers, the HBM
+roofline of the kernel, the CPU baseline (the oracle port of the reference's single-threaded CPU
+path) and, under `others`, short measurements of the path's other fused steps.
+
+With --impl reference the reference's CPU implementation of the same step (the oracle port,
+all host threads) is timed instead; nothing of the CUDA library is used.
 """
 from __future__ import annotations
 
@@ -33,11 +42,21 @@ sys.path.insert(0, ROOT)
 
 N_OUT, K_FULL = 7168, 8192
 BN = BK = 128
+VOCAB, K_HEAD = 129280, 7168
+MOE_E, MOE_K, MOE_TOPK = 384, 2048, 6
 METRIC = "us per fused GEMM+all-reduce step (o_proj, M=1)"
+REL_L2_TOL = 1e-3
+
+
+def host_cores() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 def algorithmic_bytes(m: int, n: int, k_local: int) -> int:
-    """Distinct bytes one rank must move through HBM for one step: weights + block scales
+    """Distinct bytes one rank must move through HBM for one FP8 step: weights + block scales
     + activations + reduced output (exchange slots excluded)."""
     return n * k_local + (-(-n // BN)) * (k_local // BK) * 4 + m * k_local * 2 + m * n * 4
 
@@ -49,6 +68,29 @@ def measured_peak_gbs():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def workload_config(wl: str, m: int, world: int) -> dict:
+    """The `config` object of a line; both arms print the same one for the same arguments (what a
+    run adds about itself -- how many weight sets, which timer -- goes to the line's `detail`)."""
+    common = {"l2": "consecutive steps use different weight (or route) sets, together at least 3x the device's L2 per "
+                    "rank (one set where a single shard already exceeds it): every step streams from HBM, no flush needed",
+              "timing": "K steps timed as one chain on one stream, device timers, max over ranks"}
+    if wl in ("o_proj", "shared_down"):
+        k_full = K_FULL if wl == "o_proj" else 2048
+        c = {"workload": f"{wl} fp8 [{N_OUT}x{k_full}] K/{world} per rank + fused fp32 all-reduce, M={m}",
+             "m": m, "n": N_OUT, "k": k_full, "k_per_rank": k_full // world, "parallelism": f"tp{world}"}
+    elif wl == "lm_head":
+        c = {"workload": f"lm_head fp8 [{VOCAB}x{K_HEAD}] vocab/{world} per rank + argmax candidates gathered, M={m}",
+             "m": m, "vocab": VOCAB, "k": K_HEAD, "rows_per_rank": VOCAB // world, "parallelism": f"tp{world}"}
+    elif wl == "moe_down":
+        c = {"workload": f"moe_down mxfp4 {MOE_E} experts [{N_OUT}x{MOE_K}] E/{world} per rank, top-{MOE_TOPK}, "
+                         f"+ combine + fp32 all-reduce, M={m}",
+             "m": m, "n": N_OUT, "k": MOE_K, "experts_per_rank": MOE_E // world, "parallelism": f"tp{world}"}
+    else:
+        raise SystemExit(f"unknown workload {wl}")
+    c.update(common)
+    return c
 
 
 class ClockSampler:
@@ -103,6 +145,7 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
+# ------------------------------------------------------------------------------- CPU legs
 def make_cpu_inputs(seed: int, m: int):
     """Host copy of one o_proj weight set for the CPU legs (numpy quantiser, same formats)."""
     from weightstream_b200 import formats as F, synth
@@ -110,6 +153,17 @@ def make_cpu_inputs(seed: int, m: int):
     w, sc = synth.fp8_weight(rng, N_OUT, K_FULL)
     x = F.bf16_bits_to_f32(synth.activations_bf16(rng, m, K_FULL))
     return w, sc, x
+
+
+def oracle_o_proj_step(O, w, sc, x, world: int, threads: int):
+    """The reference's CPU arithmetic for one o_proj step at tensor-parallel width `world`:
+    a block-scaled GEMV per K slice, the partial sums folded in rank order."""
+    if world == 1:
+        return O.fp8_gemv(w, sc, x, bn=BN, bk=BK, threads=threads)
+    kl = K_FULL // world
+    parts = [O.fp8_gemv(w[:, r * kl:(r + 1) * kl], sc, x[:, r * kl:(r + 1) * kl], bn=BN, bk=BK, k0=r * kl, threads=threads)
+             for r in range(world)]
+    return O.allreduce_fold(np.stack(parts))
 
 
 def time_oracle(threads: int, span_s: float, m: int = 1):
@@ -133,32 +187,77 @@ def run_reference(args) -> None:
         return
     from oracle import oracle as O
     O.build()
-    cores = O.max_threads()
-    w, sc, x = make_cpu_inputs(1234, 1)
-    step = lambda: O.fp8_gemv(w, sc, x, bn=BN, bk=BK, threads=cores)
-    for _ in range(max(1, min(args.warmup, 3))):
+    cores = host_cores()  # explicit: under torch.distributed.run OMP_NUM_THREADS is forced to 1
+    world = max(1, args.gpus)
+    w, sc, x = make_cpu_inputs(1234, args.m)
+    step = lambda: oracle_o_proj_step(O, w, sc, x, world, cores)
+    for _ in range(args.warmup):
         step()
-    steps = max(1, min(args.steps, 50))
+    steps = max(1, min(args.steps, 400))  # a bounded sample: a step takes tens of milliseconds
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
     us = (time.perf_counter() - t0) / steps * 1e6
+    one = [0.0, 0.0]
+    for i in range(2):  # the single-thread figure (what the reference engine is) beside it
+        t1 = time.perf_counter()
+        oracle_o_proj_step(O, w, sc, x, world, 1)
+        one[i] = (time.perf_counter() - t1) * 1e6
     line = {
         "impl": "reference", "metric": METRIC, "value": us, "unit": "us", "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f32 accumulate over fp8 e4m3", "data": "synthetic",
-        "config": {"workload": "o_proj fp8 [7168x8192] + rank-ordered fold, M=1, whole K on the host"},
+        "warmup": args.warmup, "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp8 e4m3 x fp8 e4m3 -> f32", "data": "synthetic",
+        "config": workload_config("o_proj", args.m, world),
         "cpu_baseline": {"value": us, "unit": "us", "cores": cores, "kind": "port",
-                         "sample": f"{steps} full steps, OpenMP over output rows (reference arithmetic, Rust original cannot be built here)"},
+                         "sample": f"{steps} full steps on the host: {world} K-slice GEMV(s) + rank-ordered fold, OpenMP over "
+                                   f"output rows on {cores} threads (reference arithmetic; the Rust original cannot be built here)",
+                         "single_thread_us": min(one)},
         "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def build_workload(args, tp, synth, torch, dev, sh, l2_bytes):
-    """Returns (step(i), e2e_step(i) or None, algorithmic bytes per launch on this rank, config dict,
-    h2d bytes, d2h bytes, endpoint)."""
-    world, rank, m, wl = sh.world_size, sh.rank, args.m, args.workload
+# ------------------------------------------------------------------------------- workloads
+class Workload:
+    """One fused step on this rank: device-resident call, host-buffer call, byte counts, and the
+    comparison of one step's result with the oracle."""
+    step = e2e = verify = None
+    abytes = 0          # algorithmic bytes of the slowest rank
+    h2d = d2h = 0
+    cfg: dict = {}
+    detail: dict = {}   # what this run adds about itself (weight sets, experts hit)
+    ep = None
+    captured_traffic = None  # DRAM bytes of one launch from the ncu capture under profiles/ (1 GPU, M=1), else None
+
+
+def same_on_all_ranks(t, world, dist, torch) -> bool:
+    if world == 1:
+        return True
+    got = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(got, t.contiguous())
+    return all(torch.equal(g.view(torch.int32), got[0].view(torch.int32)) for g in got)
+
+
+def gather_partials(part: np.ndarray, world, dist, torch, dev) -> np.ndarray:
+    t = torch.from_numpy(np.ascontiguousarray(part)).to(dev)
+    if world == 1:
+        return part[None]
+    got = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(got, t)
+    return np.stack([g.cpu().numpy() for g in got])
+
+
+def rel_l2(got: np.ndarray, want: np.ndarray) -> float:
+    d = np.linalg.norm(got.astype(np.float64) - want.astype(np.float64))
+    return float(d / max(np.linalg.norm(want.astype(np.float64)), 1e-30))
+
+
+def build_workload(wl: str, m: int, tp, synth, torch, dist, dev, sh, l2_bytes) -> Workload:
+    from oracle import oracle as O  # the checker of `verify` only; nothing timed on the GPU touches it
+    from weightstream_b200 import formats as F
+    W = Workload()
+    world, rank = sh.world_size, sh.rank
+    threads = max(1, host_cores() // world)
     g = torch.Generator(device=dev)
     g.manual_seed(99)
     if wl in ("o_proj", "shared_down"):
@@ -183,12 +282,28 @@ def build_workload(args, tp, synth, torch, dev, sh, l2_bytes):
         def e2e(i):
             ep.fp8_rowpar_gemm_allreduce_host(x_host, ws[i % layers], scs[i % layers], block=(BN, BK), k0=k0)
 
-        cfg = {"workload": f"{wl} fp8 [{N_OUT}x{k_full}] K/{world} per rank + fused fp32 all-reduce, M={m}",
-               "m": m, "n": N_OUT, "k": k_full, "k_per_rank": kl, "parallelism": f"tp{world}",
-               "l2": f"{layers} rotating weight sets ({layers * per_set / 1e6:.0f} MB per rank) > {l2_bytes / 1e6:.0f} MB L2; no flush needed"}
-        return step, e2e, algorithmic_bytes(m, N_OUT, kl), cfg, m * kl * 2, m * N_OUT * 4, ep
+        def verify():
+            out = torch.full((m, N_OUT), float("nan"), dtype=torch.float32, device=dev)
+            ep.fp8_rowpar_gemm_allreduce(x, ws[0], scs[0], block=(BN, BK), k0=k0, out=out)
+            ep.check()
+            part = O.fp8_gemv(ws[0].cpu().numpy(), scs[0].cpu().numpy(), F.bf16_bits_to_f32(x_host), bn=BN, bk=BK,
+                              k0=k0, threads=threads)
+            want = O.allreduce_fold(gather_partials(part, world, dist, torch, dev))
+            host = ep.fp8_rowpar_gemm_allreduce_host(x_host, ws[0], scs[0], block=(BN, BK), k0=k0)
+            return {"rel_l2": rel_l2(out.cpu().numpy(), want),
+                    "ranks_bit_identical": same_on_all_ranks(out, world, dist, torch),
+                    "host_call_equals_device_call": bool(np.array_equal(host.view(np.uint32), out.cpu().numpy().view(np.uint32)))}
+
+        W.cfg = workload_config(wl, m, world)
+        W.detail = {"l2": f"{layers} rotating weight sets ({layers * per_set / 1e6:.0f} MB per rank) > "
+                          f"{l2_bytes / 1e6:.0f} MB L2"}
+        W.step, W.e2e, W.verify, W.ep = step, e2e, verify, ep
+        W.abytes, W.h2d, W.d2h = algorithmic_bytes(m, N_OUT, kl), m * kl * 2, m * N_OUT * 4
+        if wl == "o_proj" and world == 1 and m == 1:
+            W.captured_traffic = 58.85e6
+        return W
     if wl == "lm_head":
-        vocab, k = 129280, 7168
+        vocab, k = VOCAB, K_HEAD
         v0, vl = sh.slice_of(vocab)
         ep = tp.Endpoint(sh, dev.index, max_m=max(m, 8), max_n=16, max_vocab=vocab, wait_ms=5000)
         # one weight set: a vocab shard is far larger than L2 at every N (116 MB at N=8 is borderline: two sets there)
@@ -216,42 +331,174 @@ def build_workload(args, tp, synth, torch, dev, sh, l2_bytes):
             arg_pin.copy_(am, non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
-        ab = vl * k + (-(-vl // BN) + 1) * (k // BK) * 4 + m * k * 2 + m * 4
-        cfg = {"workload": f"lm_head fp8 [{vocab}x{k}] vocab/{world} per rank + argmax candidates gathered, M={m}",
-               "m": m, "vocab": vocab, "k": k, "rows_per_rank": vl, "parallelism": f"tp{world}",
-               "l2": f"{sets} weight set(s) of {vl * k / 1e6:.0f} MB per rank > {l2_bytes / 1e6:.0f} MB L2"}
-        return step, e2e, ab, cfg, m * k * 2, m * 4, ep
+        def verify():
+            logits, am = ep.lm_head_allgather_argmax(x, ws[0], scs[0], vocab_row0=v0, vocab=vocab, row0=row0, want_logits=True)
+            _, am_fast = ep.lm_head_allgather_argmax(x, ws[0], scs[0], vocab_row0=v0, vocab=vocab, row0=row0, want_logits=False)
+            ep.check()
+            xf = F.bf16_bits_to_f32(x.view(torch.int16).cpu().numpy().view(np.uint16))
+            part = O.fp8_gemv(ws[0].cpu().numpy(), scs[0].cpu().numpy(), xf, bn=BN, bk=BK, row0=row0, threads=threads)
+            want = np.concatenate(list(gather_partials(part, world, dist, torch, dev)), axis=1)  # rank-ordered concatenation
+            want_arg = [O.argmax(want[t]) for t in range(m)]
+            top2 = np.sort(want, axis=1)[:, -2:]
+            return {"rel_l2": rel_l2(logits.cpu().numpy(), want),
+                    "argmax_equal": [int(a) for a in am.cpu()] == want_arg and [int(a) for a in am_fast.cpu()] == want_arg,
+                    "top1_top2_gap_min": float((top2[:, 1] - top2[:, 0]).min()),
+                    "ranks_bit_identical": same_on_all_ranks(logits, world, dist, torch) and same_on_all_ranks(am, world, dist, torch)}
+
+        W.cfg = workload_config(wl, m, world)
+        W.detail = {"l2": f"{sets} weight set(s) of {vl * k / 1e6:.0f} MB per rank > {l2_bytes / 1e6:.0f} MB L2"}
+        W.step, W.e2e, W.verify, W.ep = step, e2e, verify, ep
+        W.abytes = vl * k + (-(-vl // BN) + 1) * (k // BK) * 4 + m * k * 2 + m * 4
+        W.h2d, W.d2h = m * k * 2, m * 4
+        if world == 1 and m == 1:
+            W.captured_traffic = 934.7e6
+        return W
     if wl == "moe_down":
-        E, n, k, top_k = 384, N_OUT, 2048, 6
+        E, n, k, top_k = MOE_E, N_OUT, MOE_K, MOE_TOPK
         e0, el = sh.slice_of(E)
         ep = tp.Endpoint(sh, dev.index, max_m=max(m, 8), max_n=n, wait_ms=5000)
         w2, s2 = synth.torch_fp4_experts(el, n, k, seed=synth.config_seed(wl, 0, world) + rank, device=dev)
         rng = np.random.default_rng(synth.config_seed(wl, m, 1))
-        sets, local_experts = [], []
-        for _ in range(16):  # different routes every step: different experts stream from HBM
+        nsets = 16
+        sets, worst, mean_local = [], [], []
+        for _ in range(nsets):  # different routes every step: different experts stream from HBM
             ids, rw = synth.routes(rng, m, E, top_k)
-            sets.append((torch.from_numpy(ids).to(dev), torch.from_numpy(rw).to(dev)))
-            local_experts.append(len(np.unique(ids[(ids >= e0) & (ids < e0 + el)])))
+            sets.append((torch.from_numpy(ids).to(dev), torch.from_numpy(rw).to(dev), ids, rw))
+            per_rank = [len(np.unique(ids[(ids >= r * el) & (ids < (r + 1) * el)])) for r in range(world)]
+            worst.append(max(per_rank))       # the step ends when the busiest rank ends
+            mean_local.append(float(np.mean(per_rank)))
         h = torch.randn((m * top_k, k), generator=g, device=dev).to(torch.bfloat16)
         out = torch.empty((m, n), dtype=torch.float32, device=dev)
         h_pin, out_pin, hd = h.cpu().pin_memory(), torch.empty((m, n), dtype=torch.float32).pin_memory(), torch.empty_like(h)
 
         def step(i):
-            ep.moe_down_combine_allreduce(h, sets[i % 16][0], sets[i % 16][1], w2, s2, e0, out=out)
+            ep.moe_down_combine_allreduce(h, sets[i % nsets][0], sets[i % nsets][1], w2, s2, e0, out=out)
 
         def e2e(i):
             hd.copy_(h_pin, non_blocking=True)
-            ep.moe_down_combine_allreduce(hd, sets[i % 16][0], sets[i % 16][1], w2, s2, e0, out=out)
+            ep.moe_down_combine_allreduce(hd, sets[i % nsets][0], sets[i % nsets][1], w2, s2, e0, out=out)
             out_pin.copy_(out, non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
-        ne = float(np.mean(local_experts))
-        ab = int(ne * (n * k // 2 + n * k // 32) + m * top_k * k * 2 + m * n * 4)
-        cfg = {"workload": f"moe_down mxfp4 {E} experts [{n}x{k}] E/{world} per rank, top-{top_k}, + combine + fp32 all-reduce, M={m}",
-               "m": m, "n": n, "k": k, "experts_per_rank": el, "mean_local_experts_hit": ne, "parallelism": f"tp{world}",
-               "l2": f"16 rotating route sets over a {el * n * (k // 2 + k // 32) / 1e6:.0f} MB expert slab"}
-        return step, e2e, ab, cfg, m * top_k * k * 2, m * n * 4, ep
+        def verify():
+            o = torch.full((m, n), float("nan"), dtype=torch.float32, device=dev)
+            ep.moe_down_combine_allreduce(h, sets[0][0], sets[0][1], w2, s2, e0, out=o)
+            ep.check()
+            ids, rw = sets[0][2], sets[0][3]
+            local = np.unique(ids[(ids >= e0) & (ids < e0 + el)]) - e0
+            # only the experts this rank's routes hit leave the device
+            w2h = np.zeros((el, n, k // 2), dtype=np.uint8) if el <= 48 else None
+            if w2h is not None:
+                s2h = np.zeros((el, n, k // 32), dtype=np.uint8)
+                for e in local:
+                    w2h[e], s2h[e] = w2[e].cpu().numpy(), s2[e].cpu().numpy()
+                part = O.moe_down_combine(w2h, s2h, e0, F.bf16_bits_to_f32(h.view(torch.int16).cpu().numpy().view(np.uint16)),
+                                          ids, rw, threads=threads)
+            else:  # a slab too large to mirror on the host: remap the hit experts onto a compact slab
+                remap = {int(e): i for i, e in enumerate(local)}
+                w2h = np.stack([w2[e].cpu().numpy() for e in local]) if len(local) else np.zeros((1, n, k // 2), np.uint8)
+                s2h = np.stack([s2[e].cpu().numpy() for e in local]) if len(local) else np.zeros((1, n, k // 32), np.uint8)
+                ids2 = np.full_like(ids, -1)
+                for e, i in remap.items():  # ascending local id -> ascending compact id: the summation order is kept
+                    ids2[ids == e + e0] = i
+                part = O.moe_down_combine(w2h, s2h, 0, F.bf16_bits_to_f32(h.view(torch.int16).cpu().numpy().view(np.uint16)),
+                                          ids2, rw, threads=threads)
+            want = O.allreduce_fold(gather_partials(part, world, dist, torch, dev))
+            return {"rel_l2": rel_l2(o.cpu().numpy(), want), "ranks_bit_identical": same_on_all_ranks(o, world, dist, torch)}
+
+        per_expert = n * k // 2 + n * k // 32
+        nw = float(np.mean(worst))
+        W.cfg = workload_config(wl, m, world)
+        W.detail = {"worst_rank_experts_hit": nw, "mean_local_experts_hit": float(np.mean(mean_local)),
+                    "l2": f"{nsets} rotating route sets over a {el * per_expert / 1e6:.0f} MB expert slab"}
+        W.step, W.e2e, W.verify, W.ep = step, e2e, verify, ep
+        # bytes of the busiest rank (the step ends when it does): its experts, every route's hidden, the output
+        W.abytes = int(nw * per_expert + m * top_k * k * 2 + m * n * 4)
+        W.h2d, W.d2h = m * top_k * k * 2, m * n * 4
+        if world == 1 and m == 1:
+            W.captured_traffic = W.abytes * (47.12 / 46.79)
+        return W
     raise SystemExit(f"unknown workload {wl}")
+
+
+def time_chain(W: Workload, steps: int, warmup: int, torch, dist, world, use_graph=True):
+    """W untimed warm-up steps, then exactly `steps` steps between two CUDA events (one graph replay),
+    bracketed by a barrier and a device synchronisation; returns (ms for the K steps, launches, replay fn)."""
+    ep = W.ep
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(warmup):
+        W.step(i)
+    ep.check()
+    barrier()
+    launches0 = ep.launches
+    graph = None
+    if use_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(steps):
+                W.step(i)
+        barrier()
+        graph.replay()          # one untimed replay after capture
+        ep.check()
+    launches = ep.launches - launches0 if graph is not None else None
+
+    def run_k_steps():
+        if graph is not None:
+            graph.replay()
+        else:
+            for i in range(steps):
+                W.step(i)
+
+    if launches is None:
+        l0 = ep.launches
+        run_k_steps()
+        launches = ep.launches - l0
+    return run_k_steps, launches, barrier, graph is not None
+
+
+def quick_measure(wl, m, steps, tp, synth, torch, dist, dev, sh, l2_bytes, peak):
+    """A short measurement of another fused step for the `others` object: parity first, then a
+    graph-replayed chain timed with CUDA events (max over ranks)."""
+    world = sh.world_size
+    W = build_workload(wl, m, tp, synth, torch, dist, dev, sh, l2_bytes)
+    if world > 1:
+        W.ep.connect_process_group()
+    try:
+        parity = W.verify()
+        run, launches, barrier, _ = time_chain(W, steps, 3, torch, dist, world)
+        run()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run()
+        e1.record()
+        barrier()
+        W.ep.check()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        us = float(ms.item()) * 1e3 / steps
+        ach = W.abytes / (us * 1e-6) / 1e9
+        return {"value": us, "unit": "us", "steps": steps, "config": W.cfg, "detail": W.detail, "parity": parity,
+                "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                             "algorithmic_bytes": W.abytes},
+                "gpu_launches": int(launches)}
+    finally:
+        W.ep.close()
+        del W
+        torch.cuda.empty_cache()
+
+
+def parity_ok(p: dict) -> bool:
+    return (p.get("rel_l2", 1.0) <= REL_L2_TOL and p.get("ranks_bit_identical", False) and p.get("argmax_equal", True)
+            and p.get("host_call_equals_device_call", True))
 
 
 def run_ours(args) -> None:
@@ -275,43 +522,22 @@ def run_ours(args) -> None:
     m = args.m
     sh = tp.Sharding(world, rank)
     l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
-    step, e2e_step, abytes, cfg, h2d, d2h, ep = build_workload(args, tp, synth, torch, dev, sh, l2_bytes)
+    peak, peak_src = measured_peak_gbs()
+    W = build_workload(args.workload, m, tp, synth, torch, dist, dev, sh, l2_bytes)
+    ep = W.ep
     if world > 1:
         ep.connect_process_group()
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    # what is timed below is first checked: one step against the oracle, and rank against rank
+    parity = W.verify()
+    parity["checked"] = "one step on the first weight set before the timed region: rel-L2 against the CPU oracle " \
+                        "(per-rank oracle partials folded in rank order), output bits compared across ranks"
+    if not parity_ok(parity):
+        if rank == 0:
+            print(json.dumps({"error": "parity check failed", "parity": parity}), flush=True)
+        raise SystemExit(3)
 
-    for i in range(args.warmup):
-        step(i)
-    ep.check()
-    barrier()
-
-    # The K timed steps are captured once into a CUDA graph (K kernel nodes, one per step) and
-    # replayed, so the timed region holds kernel time, not Python call overhead.  The step
-    # sequence number lives in device memory, which is what makes the exchange replayable.
-    launches0 = ep.launches
-    graph = None
-    if not args.no_graph:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            for i in range(args.steps):
-                step(i)
-        barrier()
-        graph.replay()          # one untimed replay after capture
-        ep.check()
-    launches = ep.launches - launches0 if graph is not None else args.steps
-
-    def run_k_steps():
-        if graph is not None:
-            graph.replay()
-        else:
-            for i in range(args.steps):
-                step(i)
+    run_k_steps, launches, barrier, graphed = time_chain(W, args.steps, args.warmup, torch, dist, world, not args.no_graph)
 
     # Every rank must run the same number of steps (a step cannot finish without its peers), so
     # the length of the clock-sampling window is agreed on: one replay is timed, the slowest rank's
@@ -353,7 +579,7 @@ def run_ours(args) -> None:
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         a.record()
-        step(i)
+        W.step(i)
         b.record()
         torch.cuda.synchronize()
         iso.append(a.elapsed_time(b) * 1e3)
@@ -361,11 +587,11 @@ def run_ours(args) -> None:
     # end to end through host buffers: activations copied in, results copied out, every step
     e2e_steps = max(10, min(args.steps, 200))
     for i in range(64):  # one pass over every rotating weight set (the host-buffer call caches one graph per set)
-        e2e_step(i)
+        W.e2e(i)
     barrier()
     t0 = time.perf_counter()
     for i in range(e2e_steps):
-        e2e_step(i)
+        W.e2e(i)
     torch.cuda.synchronize()
     e2e_us = (time.perf_counter() - t0) / e2e_steps * 1e6
 
@@ -409,41 +635,55 @@ def run_ours(args) -> None:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
     ms_total, e2e_us, iso_us, iso_p99, iso_first = [float(v) for v in vals.tolist()]
     us_per_step = ms_total * 1e3 / args.steps
+    abytes, cfg, captured, detail = W.abytes, W.cfg, W.captured_traffic, dict(W.detail)
+    h2d, d2h = W.h2d, W.d2h
+    ep.close()
+    del W
+    torch.cuda.empty_cache()
+
+    # the path's other fused steps, briefly (each checked against the oracle first)
+    others = {}
+    if not args.no_others and args.workload == "o_proj" and m == 1:
+        for name, wl, om, osteps in (("o_proj_m64", "o_proj", 64, 20), ("lm_head_m1", "lm_head", 1, 8),
+                                     ("moe_down_m1", "moe_down", 1, 32)):
+            try:
+                others[name] = quick_measure(wl, om, osteps, tp, synth, torch, dist, dev, sh, l2_bytes, peak)
+            except Exception as exc:  # reported, not hidden: the headline above stands on its own
+                others[name] = {"error": f"{type(exc).__name__}: {exc}"}
 
     if rank == 0:
-        peak, peak_src = measured_peak_gbs()
         achieved = abytes / (us_per_step * 1e-6) / 1e9
-        # DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu captures
-        # summarised under profiles/ (one rank, M=1; each shows the algorithmic bytes and under 1 % more).
-        # The MoE figure depends on how many experts a step hits: the capture's ratio is applied.
-        captured = {"o_proj": 58.85e6, "lm_head": 934.7e6, "moe_down": abytes * (47.12 / 46.79)}
-        traffic = captured.get(args.workload) if (world == 1 and m == 1) else None
-        if args.workload == "o_proj":
+        if args.workload == "o_proj" and world == 1:
             cpu_us, cpu_n = time_oracle(1, 12.0, m)
             cpu = {"value": cpu_us, "unit": "us", "cores": 1, "kind": "port",
                    "sample": f"{cpu_n} full o_proj steps (M={m}, whole K), single thread as the reference engine runs"}
         else:
             cpu = None
-        cfg["timing"] = (("CUDA events around one replay of a CUDA graph holding all K steps" if graph is not None
-                          else "CUDA events around K eager launches") + ", one stream, max over ranks")
-        metric = METRIC if args.workload == "o_proj" else f"us per fused step ({args.workload}, M={m})"
+        detail["timing"] = (("CUDA events around one replay of a CUDA graph holding all K steps (a chain: consecutive steps "
+                             "overlap through programmatic dependent launch)" if graphed
+                             else "CUDA events around K eager launches") + ", one stream, max over ranks")
+        metric = METRIC if args.workload == "o_proj" and m == 1 else f"us per fused step ({args.workload}, M={m})"
         line = {
             "metric": metric, "value": us_per_step, "unit": "us", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": us_per_step / 1e3, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp8 e4m3 x fp8 e4m3 -> f32" if args.workload != "moe_down" else "fp8 e4m3 x fp4 e2m1 -> f32",
-            "data": "synthetic", "config": cfg,
+            "data": "synthetic", "config": cfg, "detail": detail,
             "isolated_us": iso_us, "isolated_p99_us": iso_p99, "isolated_first_us": iso_first,
+            "parity": parity,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "peak_source": f"of {peak_src}", "algorithmic_bytes": abytes,
+                         "traffic": captured,
+                         "traffic_source": "dram read+write bytes of one launch from the ncu capture summarised under profiles/, "
+                                           "not measured by this run" if captured is not None else None,
+                         "peak_source": f"of {peak_src}", "algorithmic_bytes": abytes,
                          "frac_of_8TBs": achieved / 8000.0},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "exchange": exchange,
+            "others": others,
         }
         print(json.dumps(line), flush=True)
-    ep.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -457,6 +697,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=1, help="activation rows per step (1 = decode)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a graph replay")
+    ap.add_argument("--no-others", action="store_true", help="skip the short measurements of the other fused steps")
     ap.add_argument("--workload", default="o_proj", choices=["o_proj", "shared_down", "moe_down", "lm_head"],
                     help="o_proj is the headline step; the others are the path's remaining fused steps")
     args = ap.parse_args()

@@ -42,7 +42,8 @@ enum {
     WS_ERR_INVALID = -1,      /* bad argument: shape, alignment, shard bounds   */
     WS_ERR_CUDA = -2,         /* a CUDA runtime / driver call failed             */
     WS_ERR_TIMEOUT = -3,      /* a peer's partial did not arrive within wait_ms  */
-    WS_ERR_SEQUENCE = -4,     /* endpoints of a group disagree on the step count */
+    WS_ERR_SEQUENCE = -4,     /* ranks disagree on the step count (host check, or a peer's
+                                 partial tagged with a later step: ring.rs:488-499)          */
     WS_ERR_CAPACITY = -5,     /* the step exceeds what the endpoint was sized for */
     WS_ERR_UNSUPPORTED = -6
 };
@@ -182,8 +183,7 @@ ws_status_t ws_act_quant_fp8(const void *x, int64_t ldx, int32_t x_dtype, int32_
 
 /* Scheduling knob with no counterpart in the reference: 1 (default) deals the output rows
  * that do not fill whole 16-row tiles on every CTA out row by row, so that every SM streams
- * the same number of bytes; 0 hands each leftover tile to one CTA whole.  Bit 2 set
- * (on = 4 or 5) turns programmatic dependent launch off. */
+ * the same number of bytes; 0 hands each leftover tile to one CTA whole. */
 ws_status_t ws_tp_set_split(ws_tp_t *tp, int32_t on);
 /* Kernel choice, also without counterpart in the reference.  0 (default) automatic: FP8 steps
  * run one or two activation rows on CUDA cores and three or more through the tensor-core MMA,
@@ -210,12 +210,19 @@ ws_status_t ws_tp_set_kernel(ws_tp_t *tp, int32_t which);
  *    shared-memory limit; make that first call before any stream capture begins.
  *  - all calls on a device share the one array, which keeps the previous call's contents; the
  *    entry point clears the counters and the status word on `stream` before the kernel.  Two
- *    calls that overlap on the GPU (different streams, no ordering) race on it. */
+ *    calls that overlap on the GPU (different streams, no ordering) race on it.
+ *  - both functions make `device` the calling thread's current device and leave it so.
+ *  - the launch is asynchronous and returns WS_OK once enqueued.  A bounded wait inside the kernel
+ *    that gives up (a weight tile that never lands) is recorded in the array's status word, which
+ *    the next call clears: call ws_fp8_gemm_static_scratch_check after the launch -- it
+ *    synchronises `stream`, reads the word (4 bytes, no allocation) and returns WS_OK or the
+ *    recorded error with its text in `err` -- before trusting `out`. */
 #define WS_STATIC_MAX_M 8
 #define WS_STATIC_MAX_N 1048576
 #define WS_STATIC_SCRATCH_BYTES 1024
 ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *args, int32_t device, void *stream,
                                        char *err, size_t err_len);
+ws_status_t ws_fp8_gemm_static_scratch_check(int32_t device, void *stream, char *err, size_t err_len);
 
 const char *ws_version(void);
 

@@ -71,6 +71,10 @@ def _declare(L: C.CDLL) -> None:
     L.wso_f32_to_bf16.argtypes = [C.c_float]
     L.wso_f32_to_e4m3.restype = C.c_uint8
     L.wso_f32_to_e4m3.argtypes = [C.c_float]
+    L.wso_set_e4m3_literal.restype = None
+    L.wso_set_e4m3_literal.argtypes = [C.c_int]
+    L.wso_get_e4m3_literal.restype = C.c_int
+    L.wso_get_e4m3_literal.argtypes = []
     L.wso_f32_to_e2m1.restype = C.c_uint8
     L.wso_f32_to_e2m1.argtypes = [C.c_float]
     L.wso_fp8_snap.restype = None
@@ -142,6 +146,22 @@ def f32_to_bf16(v: float) -> int:
 
 def f32_to_e4m3(v: float) -> int:
     return int(lib().wso_f32_to_e4m3(v))
+
+
+class e4m3_literal:
+    """Context manager: inside it the E4M3 encoder returns what
+    crates/weightstream-core/src/quant.rs:121 returns as written (the byte of 1.0 for
+    |v| in [7.5/512, 8/512)) instead of the byte of 2^-6 that the reference's device
+    encoder (crates/weightstream-cuda/kernels/common.cuh:26) and round-to-nearest give."""
+
+    def __enter__(self):
+        self.prev = int(lib().wso_get_e4m3_literal())
+        lib().wso_set_e4m3_literal(1)
+        return self
+
+    def __exit__(self, *exc):
+        lib().wso_set_e4m3_literal(self.prev)
+        return False
 
 
 def f32_to_e2m1(v: float) -> int:

@@ -67,9 +67,24 @@ uint16_t wso_f32_to_bf16(float v) {
     return (uint16_t)((bits + round) >> 16);
 }
 
+/* Which byte a magnitude in [7.5/512, 8/512) -- the top of the subnormal range, which
+ * rounds up to the smallest normal 2^-6 -- encodes to.  The reference has two answers:
+ *   0 (default): 0x08, the byte of 2^-6 (E=1, M=0).  This is what the reference's device
+ *      encoder returns (crates/weightstream-cuda/kernels/common.cuh:26), what its comment at
+ *      crates/weightstream-core/src/quant.rs:121 says it means, and what round-to-nearest-even
+ *      onto the E4M3 grid is.
+ *   1: 0x38, the byte of 1.0, which is what crates/weightstream-core/src/quant.rs:121
+ *      returns as written ("sign | 0x38"); no reference test reaches that branch
+ *      (quant.rs:285-306 only round-trips exact grid points and three ties below it).
+ * Everything else in the encoder is identical in both modes. */
+static int g_e4m3_literal_quant_rs = 0;
+void wso_set_e4m3_literal(int on) { g_e4m3_literal_quant_rs = on ? 1 : 0; }
+int wso_get_e4m3_literal(void) { return g_e4m3_literal_quant_rs; }
+
 /* crates/weightstream-core/src/quant.rs:106-137: RNE onto the E4M3 grid,
  * saturating at +-448, NaN -> S.1111.111. nearbyintf under the default rounding
- * mode is round-half-to-even, as round_ties_even is. */
+ * mode is round-half-to-even, as round_ties_even is.  Line 121 is followed in the
+ * sense of the mode above. */
 uint8_t wso_f32_to_e4m3(float v) {
     uint32_t bits = f2u(v);
     uint8_t sign = (uint8_t)((bits >> 24) & 0x80);
@@ -79,7 +94,7 @@ uint8_t wso_f32_to_e4m3(float v) {
     if (a < wso_pow2i(-6)) {
         float q = a * 512.0f;
         int m = (int)nearbyintf(q);
-        if (m == 8) return sign | 0x08; /* 2^-6: E=1, M=0 */
+        if (m == 8) return sign | (g_e4m3_literal_quant_rs ? 0x38 : 0x08); /* 2^-6: E=1, M=0 */
         return sign | (uint8_t)m;
     }
     int e = (int)((bits >> 23) & 0xFF) - 127;

@@ -8,7 +8,9 @@
  * benchmark's cpu_baseline / reference arm may load it.
  *
  * Parity status: pinned against every known-answer value the reference's own
- * unit tests hold for these functions (see the per-function citations); the
+ * unit tests hold for these functions (see the per-function citations), with one
+ * recorded departure: the E4M3 encoder's answer for |v| in [7.5/512, 8/512), where the
+ * reference's CPU and device encoders disagree (wso_set_e4m3_literal below); the
  * 128x128-fp32-scale FP8 form, the FP8 lm_head and world sizes other than 4 are
  * not covered by any reference test and are pinned by this restatement only.
  * The Rust original cannot be compiled in the build environment (no cargo/rustc).
@@ -33,6 +35,11 @@ float    wso_ue8m0_round_scale(float amax, float fp_max); /* quant.rs:85 */
 float    wso_bf16_to_f32(uint16_t bits);             /* quant.rs:91  */
 uint16_t wso_f32_to_bf16(float v);                   /* quant.rs:97  */
 uint8_t  wso_f32_to_e4m3(float v);                   /* quant.rs:106 */
+/* quant.rs:121 as written returns the byte of 1.0 for |v| in [7.5/512, 8/512); the reference's
+ * device encoder (kernels/common.cuh:26) returns the byte of 2^-6.  0 (default) follows the device
+ * encoder, 1 follows quant.rs:121 to the letter.  Process-wide; not thread-safe to flip mid-call. */
+void     wso_set_e4m3_literal(int on);
+int      wso_get_e4m3_literal(void);
 uint8_t  wso_f32_to_e2m1(float v);                   /* quant.rs:141 */
 
 /* ---- activation quantisation: crates/weightstream-ref/src/actquant.rs:21-57 ---- */

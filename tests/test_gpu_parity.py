@@ -300,6 +300,32 @@ def test_wait_times_out_and_context_survives(dev, tpmod):
         grp.close()
 
 
+def test_peer_that_ran_ahead_is_a_sequence_error(dev, tpmod):
+    """crates/weightstream-transport/src/ring.rs:488-499: an immediate whose step is neither this
+    step's nor an earlier one aborts the collective ("out of sequence").  Rank 1 of a two-rank group
+    takes three steps on its own (each gives up after wait_ms, as above) and so leaves words tagged
+    with step 3 in rank 0's slots; rank 0's first step must then report WS_ERR_SEQUENCE, not wait
+    for a time-out, and the device must stay usable."""
+    grp = tpmod.LocalGroup(2, max_m=1, max_n=256, wait_ms=20)
+    try:
+        v = torch.ones(256, device=dev)
+        out = torch.empty_like(v)
+        ep0, ep1 = grp.eps
+        for _ in range(3):
+            ep1._ok(ep1.lib.ws_allreduce_f32(ep1.handle, v.data_ptr(), out.data_ptr(), 256, tpmod._stream_ptr()))
+            with pytest.raises(tpmod.WsError) as ei:
+                ep1.check()
+            assert ei.value.status == tpmod._lib.WS_ERR_TIMEOUT
+        ep0._ok(ep0.lib.ws_allreduce_f32(ep0.handle, v.data_ptr(), out.data_ptr(), 256, tpmod._stream_ptr()))
+        with pytest.raises(tpmod.WsError) as ei:
+            ep0.check()
+        assert ei.value.status == tpmod._lib.WS_ERR_SEQUENCE, ei.value
+        assert "out of sequence" in str(ei.value)
+        assert float((v + 1).sum().item()) == 512.0  # the context still works
+    finally:
+        grp.close()
+
+
 # ----------------------------------------------------------------------------- lm_head
 @pytest.mark.parametrize("world", [1, 2, 8])
 @pytest.mark.parametrize("m", [1, 2, 3, 20])  # CUDA-core form (1, 2), MMA form (3), all rows in one wide launch (20)

@@ -69,6 +69,56 @@ def test_e4m3_encode_roundtrip_and_ties(oracle):
     assert oracle.f32_to_e4m3(2.5 / 512.0) == 0x02
 
 
+def test_e4m3_top_of_subnormal_range_the_two_reference_answers(oracle):
+    """|v| in [7.5/512, 8/512) rounds up to the smallest normal, 2^-6 = byte 0x08.  The
+    reference's device encoder returns that byte (crates/weightstream-cuda/kernels/common.cuh:26),
+    its CPU encoder returns 0x38 = 1.0 as written (crates/weightstream-core/src/quant.rs:121;
+    the comment beside it says "2^-6 = E=1 M=0", no reference test reaches the branch).  The
+    oracle follows the device encoder by default -- so does cvt.rn.satfinite.e4m3x2.f32 on the
+    GPU -- and reproduces the CPU encoder's byte on request; both are pinned here."""
+    for v, dev_byte, cpu_byte in [(7.75 / 512, 0x08, 0x38), (-7.75 / 512, 0x88, 0xB8),
+                                  (7.5 / 512, 0x08, 0x38), (np.float32(8 / 512 - 2.0 ** -30), 0x08, 0x38)]:
+        assert oracle.f32_to_e4m3(float(v)) == dev_byte
+        with oracle.e4m3_literal():
+            assert oracle.f32_to_e4m3(float(v)) == cpu_byte
+        assert oracle.f32_to_e4m3(float(v)) == dev_byte  # the switch is restored
+    assert oracle.e4m3_to_f32(0x08) == 2.0 ** -6 and oracle.e4m3_to_f32(0x38) == 1.0
+    # just outside the interval both agree
+    for v in [np.float32(7.5 / 512 - 2.0 ** -30), 8 / 512, 7.0 / 512]:
+        a = oracle.f32_to_e4m3(float(v))
+        with oracle.e4m3_literal():
+            assert oracle.f32_to_e4m3(float(v)) == a
+
+
+def test_quant_rs_121_as_written_stays_within_the_path_tolerance(oracle):
+    """The o_proj configuration (x ~ N(0,1) bf16 [*, 8192], W FP8 [7168 x 8192], 128x128 fp32
+    scales) through the oracle twice: with the E4M3 encoder of the reference's device path (the
+    default, what the CUDA library computes) and with crates/weightstream-core/src/quant.rs:121
+    to the letter (what weightstream-ref computes).  Activations landing in the affected interval
+    are rare (a few per million) but each becomes 64 times too large; the outputs must still agree
+    within the path's stated tolerance of 1e-3 relative L2, row by row."""
+    from weightstream_b200 import formats as F, synth
+    rng = np.random.default_rng(synth.config_seed("o_proj", 1, 1))
+    n, k, m = 7168, 8192, 24
+    w, sc = synth.fp8_weight(rng, n, k)
+    xf = F.bf16_bits_to_f32(synth.activations_bf16(rng, m, k))
+    thr = oracle.max_threads()
+    dev = oracle.fp8_gemv(w, sc, xf, bn=128, bk=128, threads=thr)
+    snap_dev = np.stack([oracle.fp8_snap(r) for r in xf])
+    with oracle.e4m3_literal():
+        cpu = oracle.fp8_gemv(w, sc, xf, bn=128, bk=128, threads=thr)
+        snap_cpu = np.stack([oracle.fp8_snap(r) for r in xf])
+    hit_rows = np.flatnonzero((snap_dev != snap_cpu).any(axis=1))
+    assert hit_rows.size >= 1, "the sample should contain at least one affected activation"
+    worst = 0.0
+    for r in range(m):
+        d = np.linalg.norm(dev[r].astype(np.float64) - cpu[r]) / np.linalg.norm(cpu[r].astype(np.float64))
+        worst = max(worst, d)
+        if r not in hit_rows:
+            assert d == 0.0
+    assert 0.0 < worst < 1e-3, worst
+
+
 def test_e2m1_encode_ties(oracle):
     # crates/weightstream-core/src/quant.rs:309-330
     for code in range(16):

@@ -29,7 +29,7 @@ EXPORTS = [
     "ws_lm_head_allgather_argmax", "ws_lm_head_allgather_argmax_group",
     "ws_allreduce_f32", "ws_allgather_f32", "ws_allreduce_f32_group", "ws_allgather_f32_group",
     "ws_allreduce_f32_host", "ws_allgather_f32_host", "ws_fp8_rowpar_gemm_allreduce_host",
-    "ws_act_quant_fp8", "ws_tp_set_split", "ws_tp_set_kernel", "ws_fp8_gemm_static_scratch", "ws_version",
+    "ws_act_quant_fp8", "ws_tp_set_split", "ws_tp_set_kernel", "ws_fp8_gemm_static_scratch", "ws_fp8_gemm_static_scratch_check", "ws_version",
 ]
 
 
@@ -148,5 +148,7 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     L.ws_tp_set_kernel.argtypes = [P, C.c_int32]
     L.ws_fp8_gemm_static_scratch.restype = st
     L.ws_fp8_gemm_static_scratch.argtypes = [C.POINTER(Fp8GemmArgs), C.c_int32, P, C.c_char_p, C.c_size_t]
+    L.ws_fp8_gemm_static_scratch_check.restype = st
+    L.ws_fp8_gemm_static_scratch_check.argtypes = [C.c_int32, P, C.c_char_p, C.c_size_t]
     _lib = L
     return L

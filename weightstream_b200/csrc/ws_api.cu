@@ -9,6 +9,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/ws_tp.h"
@@ -51,7 +52,7 @@ struct ws_tp {
         uint64_t steps = 0, launches = 0, used = 0;
         cudaGraphExec_t exec = nullptr;
     };
-    std::vector<HostGraph> hgraphs;
+    std::unordered_map<uint64_t, HostGraph> hgraphs;  // keyed by a hash of the argument set
     uint32_t *pin_status = nullptr;
     uint64_t hgraph_clock = 0;
     // MoE decode step: routes quantised once per step, pass table, large-m accumulators
@@ -126,6 +127,24 @@ int ragged_granularity(int n, int ncta) {
     const int L = n - Gm * ncta * kGroupRows;
     const int per = L / ncta;  // whole rows per CTA
     return per >= 8 ? 4 : per >= 4 ? 2 : 1;
+}
+
+// Text for a non-zero device status word (detail code in the high byte, -WS_ERR_* in the low byte).
+std::string describe_status(uint32_t st, uint64_t timeout_ns) {
+    const uint32_t where = st >> 24;
+    char buf[256];
+    if (where == (kStatRunAhead >> 24)) {
+        snprintf(buf, sizeof buf, "collective out of sequence: a peer's partial carries a later step than this rank's; "
+                                  "fail-stop, results invalid");
+    } else {
+        const char *what = where == 1   ? "a peer CTA's partial"
+                           : where == 3 ? "a weight tile (TMA)"
+                           : where == 4 ? "the gather of every rank"
+                                        : "an unknown event";
+        snprintf(buf, sizeof buf, "wait for %s timed out after %llu ms; fail-stop, results invalid", what,
+                 (unsigned long long)(timeout_ns / 1000000ull));
+    }
+    return buf;
 }
 
 RankCtx make_ctx(const ws_tp *tp) {
@@ -258,7 +277,7 @@ ws_status_t ws_tp_destroy(ws_tp_t *tp) {
     if (tp->pin) cudaFreeHost(tp->pin);
     if (tp->dev_stage) cudaFree(tp->dev_stage);
     for (auto &g : tp->hgraphs)
-        if (g.exec) cudaGraphExecDestroy(g.exec);
+        if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     if (tp->pin_status) cudaFreeHost(tp->pin_status);
     if (tp->moe_work) cudaFree(tp->moe_work);
     if (tp->moe_acc) cudaFree(tp->moe_acc);
@@ -338,13 +357,7 @@ ws_status_t ws_tp_check(ws_tp_t *tp, void *stream) {
     WS_CUDA(tp, cudaMemcpy(&st, tp->status, 4, cudaMemcpyDeviceToHost));
     if (st == 0) return WS_OK;
     WS_CUDA(tp, cudaMemset(tp->status, 0, 4));
-    const uint32_t where = st >> 24;
-    const char *what = where == 1   ? "a peer CTA's partial"
-                       : where == 3 ? "a weight tile (TMA)"
-                       : where == 4 ? "the gather of every rank"
-                                    : "an unknown event";
-    return fail(tp, -(ws_status_t)(st & 0xFFu), "rank %d: wait for %s timed out after %llu ms; fail-stop, results invalid",
-                tp->rank, what, (unsigned long long)(tp->timeout_ns / 1000000ull));
+    return fail(tp, -(ws_status_t)(st & 0xFFu), "rank %d: %s", tp->rank, describe_status(st, tp->timeout_ns).c_str());
 }
 
 const char *ws_tp_last_error(ws_tp_t *tp) { return tp ? tp->err.c_str() : "null endpoint"; }
@@ -937,6 +950,21 @@ ws_status_t ws_allgather_f32_host(ws_tp_t *tp, const float *in, float *out, int6
 // The host-buffer step is the same sequence every time a caller repeats it on one weight (copy
 // the activations in, launch, copy the rows and the status word out), so it is captured once per
 // distinct argument set and replayed as one graph launch; a handful of sets are kept.
+static uint64_t hash_fp8_args(const ws_fp8_gemm_args_t &a, const void *pin, const void *dev, int sel) {
+    uint64_t h = 0xcbf29ce484222325ull;  // FNV-1a over the fields that name a distinct step
+    auto mix = [&](uint64_t v) {
+        for (int i = 0; i < 8; ++i) {
+            h ^= (v >> (8 * i)) & 0xFFu;
+            h *= 0x100000001b3ull;
+        }
+    };
+    mix((uint64_t)(uintptr_t)a.w); mix((uint64_t)(uintptr_t)a.scales); mix((uint64_t)a.ldw); mix((uint64_t)a.scale_ld);
+    mix(((uint64_t)(uint32_t)a.m << 32) | (uint32_t)a.n); mix(((uint64_t)(uint32_t)a.k << 32) | (uint32_t)a.x_dtype);
+    mix(((uint64_t)(uint32_t)a.block_n << 32) | (uint32_t)a.block_k); mix((uint64_t)a.row0); mix((uint64_t)a.k0);
+    mix((uint64_t)(uintptr_t)pin); mix((uint64_t)(uintptr_t)dev); mix(((uint64_t)(uint32_t)a.scale_kind << 32) | (uint32_t)sel);
+    return h;
+}
+
 static bool same_fp8_args(const ws_fp8_gemm_args_t &a, const ws_fp8_gemm_args_t &b) {
     return a.m == b.m && a.n == b.n && a.k == b.k && a.x_dtype == b.x_dtype && a.w == b.w && a.ldw == b.ldw &&
            a.scales == b.scales && a.scale_ld == b.scale_ld && a.scale_kind == b.scale_kind && a.block_n == b.block_n &&
@@ -957,10 +985,20 @@ ws_status_t ws_fp8_rowpar_gemm_allreduce_host(ws_tp_t *tp, const ws_fp8_gemm_arg
     a.out = reinterpret_cast<float *>(dev + xb_al);
 
     ws_tp::HostGraph *hit = nullptr;
-    for (auto &g : tp->hgraphs)
-        if (g.exec && g.pin == pin && g.dev == dev && g.kernel_sel == tp->kernel_sel && g.split == tp->split &&
-            g.pdl == tp->pdl && same_fp8_args(g.key, a))
-            hit = &g;
+    const uint64_t hkey = hash_fp8_args(a, pin, dev, tp->kernel_sel * 4 + tp->split * 2 + tp->pdl);
+    {
+        auto it = tp->hgraphs.find(hkey);
+        if (it != tp->hgraphs.end()) {
+            ws_tp::HostGraph &g = it->second;
+            if (g.exec && g.pin == pin && g.dev == dev && g.kernel_sel == tp->kernel_sel && g.split == tp->split &&
+                g.pdl == tp->pdl && same_fp8_args(g.key, a)) {
+                hit = &g;
+            } else {  // a hash collision or a re-sized staging buffer: the stale graph goes
+                if (g.exec) cudaGraphExecDestroy(g.exec);
+                tp->hgraphs.erase(it);
+            }
+        }
+    }
     if (!hit) {  // capture; any failure falls back to plain enqueueing below
         const uint64_t step0 = tp->step, launches0 = tp->launches;
         cudaGraph_t graph = nullptr;
@@ -980,16 +1018,14 @@ ws_status_t ws_fp8_rowpar_gemm_allreduce_host(ws_tp_t *tp, const ws_fp8_gemm_arg
         tp->launches = launches0;
         cudaGetLastError();
         if (ok && exec) {
-            ws_tp::HostGraph *slot = nullptr;
-            if (tp->hgraphs.size() < 256) {  // one per weight a caller cycles through (a model's layers)
-                tp->hgraphs.emplace_back();
-                slot = &tp->hgraphs.back();
-            } else {
-                slot = &tp->hgraphs[0];
-                for (auto &g : tp->hgraphs)
-                    if (g.used < slot->used) slot = &g;
-                if (slot->exec) cudaGraphExecDestroy(slot->exec);
+            if (tp->hgraphs.size() >= 1024) {  // one per weight a caller cycles through; evict the least recently used
+                auto old = tp->hgraphs.begin();
+                for (auto it = tp->hgraphs.begin(); it != tp->hgraphs.end(); ++it)
+                    if (it->second.used < old->second.used) old = it;
+                if (old->second.exec) cudaGraphExecDestroy(old->second.exec);
+                tp->hgraphs.erase(old);
             }
+            ws_tp::HostGraph *slot = &tp->hgraphs[hkey];
             slot->key = a; slot->pin = pin; slot->dev = dev;
             slot->kernel_sel = tp->kernel_sel; slot->split = tp->split; slot->pdl = tp->pdl;
             slot->steps = steps; slot->launches = launches; slot->exec = exec;
@@ -1035,12 +1071,10 @@ ws_status_t ws_tp_set_kernel(ws_tp_t *tp, int32_t which) {
     return WS_OK;
 }
 
-// Testing knob: 0 makes the leftover row groups whole-CTA work instead of K-split work.
+// 1 (default): leftover rows are dealt out row by row; 0: each leftover tile goes to one CTA whole.
 ws_status_t ws_tp_set_split(ws_tp_t *tp, int32_t on) {
     if (!tp) return WS_ERR_INVALID;
-    tp->split = on < 0 ? 0 : (on > 2 ? 2 : on);
-    tp->pdl = (on & 4) ? 0 : 1;  // bit 2 switches programmatic dependent launch off (measurement aid)
-    tp->split &= 3;
+    tp->split = on ? 1 : 0;
     return WS_OK;
 }
 
@@ -1149,9 +1183,26 @@ ws_status_t ws_fp8_gemm_static_scratch(const ws_fp8_gemm_args_t *a, int32_t devi
     return WS_OK;
 }
 
-#ifdef WS_TRACE
-void ws_debug_read_trace(unsigned long long *out) { cudaMemcpyFromSymbol(out, g_ws_trace, sizeof(g_ws_trace)); }
-void ws_debug_read_trace2(unsigned long long *out) { cudaMemcpyFromSymbol(out, g_ws_trace2, sizeof(g_ws_trace2)); }
-#endif
+// Completion check for ws_fp8_gemm_static_scratch: the kernel records a bounded wait that gave up
+// in the scratch array's status word; this reads it back (no allocation: a stream synchronise and
+// a 4-byte copy into a local) and turns it into a status, as ws_tp_check does for an endpoint.
+ws_status_t ws_fp8_gemm_static_scratch_check(int32_t device, void *stream, char *err, size_t err_len) {
+    if (err && err_len) err[0] = 0;
+    if (device < 0 || device >= kStaticMaxDevices) { set_err(err, err_len, "device %d out of range", device); return WS_ERR_INVALID; }
+    unsigned char *base;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        base = g_static_scratch_addr[device];
+    }
+    if (!base) { set_err(err, err_len, "ws_fp8_gemm_static_scratch has not run on device %d", device); return WS_ERR_INVALID; }
+    cudaError_t ce = cudaSetDevice(device);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    uint32_t st = 0;
+    if (ce == cudaSuccess) ce = cudaMemcpy(&st, base + kMaxShared * sizeof(uint32_t), sizeof st, cudaMemcpyDeviceToHost);
+    if (ce != cudaSuccess) { set_err(err, err_len, "reading the status word: %s", cudaGetErrorString(ce)); return WS_ERR_CUDA; }
+    if (st == 0) return WS_OK;
+    set_err(err, err_len, "%s", describe_status(st, 2000000000ull).c_str());
+    return -(ws_status_t)(st & 0xFFu);
+}
 
 }  // extern "C"

@@ -15,10 +15,7 @@ constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;  // + one TMA producer warp
 constexpr int kBoxBytes = 2048;                  // one TMA box: 16 rows x 128 bytes
-#ifndef WS_BOXES_PER_STAGE
-#define WS_BOXES_PER_STAGE 16
-#endif
-constexpr int kBoxesPerStage = WS_BOXES_PER_STAGE;
+constexpr int kBoxesPerStage = 16;
 constexpr int kStageBytes = kBoxBytes * kBoxesPerStage;  // 32 KB
 constexpr int kMaxStages = 16;
 constexpr int kMaxCtas = 160;    // persistent CTAs per rank (one per SM on B200: 148)
@@ -30,7 +27,8 @@ enum : uint32_t {
     kStatOk = 0,
     kStatTimeoutPeerA = 0x01000000u,  // waiting for a peer CTA's owned-rows flag
     kStatTimeoutTma = 0x03000000u,    // a weight tile never landed in shared memory
-    kStatTimeoutGather = 0x04000000u
+    kStatTimeoutGather = 0x04000000u,
+    kStatRunAhead = 0x05000000u       // a peer's word or flag carries a later step than this rank's
 };
 
 // ---------------------------------------------------------------- exchange layout
@@ -94,12 +92,8 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-#ifndef WS_WAIT_MODE
-#define WS_WAIT_MODE 0
-#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-#if WS_WAIT_MODE == 0
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
@@ -107,30 +101,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok)
         : "r"(bar), "r"(parity), "r"(20000u)  // the thread may sleep until the phase completes (at most ~20 us per probe)
         : "memory");
-#elif WS_WAIT_MODE == 1
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-#else
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-#endif
     return ok != 0;
 }
 // Bounded wait: gives up after two seconds of wall time (globaltimer), records why, and lets the
-// caller unwind instead of spinning forever.
+// caller unwind instead of spinning forever.  Once any wait of the launch has failed (the status
+// word is set) every later wait that is not satisfied at once returns false immediately, so a
+// kernel with hundreds of stage waits ends in one time-out, not hundreds.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *status) {
     for (int i = 0; i < 64; ++i)
         if (mbar_try_wait(bar, parity)) return true;
+    if (*(volatile uint32_t *)status != 0u) return false;
     const uint64_t t0 = globaltimer_ns();
     for (;;) {
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
+        if (*(volatile uint32_t *)status != 0u) return false;
         if (globaltimer_ns() - t0 > 2000000000ull) break;
     }
     atomicCAS(status, 0u, kStatTimeoutTma | (uint32_t)(-WS_ERR_TIMEOUT));
@@ -281,16 +266,31 @@ __device__ __forceinline__ uint64_t ld_volatile_u64(const uint64_t *p) {
     return v;
 }
 
+// A tag that is ahead of this rank's step: the peer ran on without this rank (the reference aborts
+// on an immediate whose sequence is neither this step's nor an earlier one,
+// crates/weightstream-transport/src/ring.rs:488-499).  Tags compare modulo 2^32.
+__device__ __forceinline__ bool tag_ahead(uint32_t tag, uint32_t seq) { return (int32_t)(tag - seq) > 0; }
+__device__ __forceinline__ void record_run_ahead(uint32_t *status) {
+    atomicCAS(status, 0u, kStatRunAhead | (uint32_t)(-WS_ERR_SEQUENCE));
+}
+
 // Poll `flag` until it carries `seq`.  Every wait is bounded by `timeout_ns`: on
 // expiry the first error is recorded in *status and the caller returns normally
-// (fail-stop at the host, never a trap or an endless spin).
+// (fail-stop at the host, never a trap or an endless spin).  A flag from a later step is an
+// error of its own (WS_ERR_SEQUENCE) and ends the wait at once.
 __device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t seq, uint64_t timeout_ns,
                                           uint32_t *status, uint32_t code) {
-    if (ld_acquire_sys(flag) == seq) return true;
+    uint32_t f = ld_acquire_sys(flag);
+    if (f == seq) return true;
     const uint64_t t0 = globaltimer_ns();
     for (;;) {
         for (int i = 0; i < 32; ++i) {
-            if (ld_acquire_sys(flag) == seq) return true;
+            f = ld_acquire_sys(flag);
+            if (f == seq) return true;
+        }
+        if (tag_ahead(f, seq)) {
+            record_run_ahead(status);
+            return false;
         }
         if (globaltimer_ns() - t0 > timeout_ns) {
             atomicCAS(status, 0u, code | (uint32_t)(-WS_ERR_TIMEOUT));
@@ -312,7 +312,8 @@ __device__ __forceinline__ uint64_t ld_word_sys(const uint64_t *p) {
     asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
-// Bounded like wait_flag; returns 0 when the wait gave up (the status word then says so).
+// Bounded like wait_flag (time-out and run-ahead detection); returns 0 when the wait gave up (the
+// status word then says why).
 __device__ __forceinline__ float wait_word(const uint64_t *p, uint32_t seq, uint64_t timeout_ns, uint32_t *status,
                                            uint32_t code) {
     uint64_t w = ld_word_sys(p);
@@ -322,6 +323,10 @@ __device__ __forceinline__ float wait_word(const uint64_t *p, uint32_t seq, uint
         for (int i = 0; i < 32; ++i) {
             w = ld_word_sys(p);
             if ((uint32_t)(w >> 32) == seq) return __uint_as_float((uint32_t)w);
+        }
+        if (tag_ahead((uint32_t)(w >> 32), seq)) {
+            record_run_ahead(status);
+            return 0.0f;
         }
         if (globaltimer_ns() - t0 > timeout_ns) {
             atomicCAS(status, 0u, code | (uint32_t)(-WS_ERR_TIMEOUT));

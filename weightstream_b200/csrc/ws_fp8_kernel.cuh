@@ -33,18 +33,6 @@ namespace ws {
 
 enum { kModeAllReduce = 0, kModeLmHead = 1 };
 
-#ifdef WS_TRACE  // phase timestamps per CTA, for a probe build only
-__device__ unsigned long long g_ws_trace[kMaxCtas][8];
-#define WS_MARK(i) do { if (threadIdx.x == 0) g_ws_trace[blockIdx.x][i] = globaltimer_ns(); } while (0)
-#define WS_MARK_T(i, t) do { if (threadIdx.x == (t)) g_ws_trace[blockIdx.x][i] = globaltimer_ns(); } while (0)
-__device__ unsigned long long g_ws_trace2[256];  // fine-grained marks of CTA 0
-#define WS_MARK2(i) do { if (blockIdx.x == 0 && (i) < 256) g_ws_trace2[i] = globaltimer_ns(); } while (0)
-#else
-#define WS_MARK2(i) do { } while (0)
-#define WS_MARK(i) do { } while (0)
-#define WS_MARK_T(i, t) do { } while (0)
-#endif
-
 struct Fp8RankArgs {
     const void *x;
     const void *scales;
@@ -73,10 +61,7 @@ struct alignas(64) Fp8Params {
 
 // Consumer warps per CTA.  Sixteen warps instead of eight changed neither formulation's time by
 // more than 2 % on B200, so both run eight.
-#ifndef WS_GEMV_WARPS
-#define WS_GEMV_WARPS 8
-#endif
-__host__ __device__ constexpr int fp8_consumer_warps(int gt) { return gt > 0 ? WS_GEMV_WARPS : kConsumerWarps; }
+__host__ __device__ constexpr int fp8_consumer_warps(int) { return kConsumerWarps; }
 __host__ __device__ constexpr int fp8_threads(int gt) { return (fp8_consumer_warps(gt) + 1) * 32; }  // + the TMA producer warp
 
 struct Fp8Smem {  // byte offsets from the 1024-aligned base
@@ -173,7 +158,6 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     const uint32_t stage0 = smem_u32(smem + S.stages);
     const uint32_t full0 = smem_u32(smem + S.bars), empty0 = full0 + kMaxStages * 8;
     const int NS = p.nstages;
-    WS_MARK(0);
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
@@ -197,7 +181,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
             for (int b0 = 0; b0 < kbox; b0 += cols) {
                 const int nb = min(cols, kbox - b0);
                 const int s = rp.s;
-                mbar_wait(empty0 + s * 8, rp.ph ^ 1u, X.status);
+                if (!mbar_wait(empty0 + s * 8, rp.ph ^ 1u, X.status)) return;  // a wait gave up: stop streaming
                 if (lane == 0) mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)(nb * cnt * 128));
                 __syncwarp();
                 for (int col = lane; col < nb; col += 32) {
@@ -219,11 +203,9 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     // Everything below may read what the previous kernel on the stream wrote (activations, the
     // step sequence, exchange slots): wait for it.  The producer warp above streams weights,
     // which are static, and does not wait.
-    if (tid == 0) WS_MARK2(0);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t seq = step_begin(X);
     const uint32_t bank = seq & 1u;
-    if (tid == 0) WS_MARK2(1);
     // Prologue: weight scales of the rows this CTA touches (loads issued first, stored last, so
     // their latency overlaps the activation loads), then the activation quantisation.
     // q_s[kb][tok][32] holds E4M3 bytes, sa_s[kb][tok(sast)] the block scale 2^e.
@@ -255,10 +237,8 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
             const int i = tid + u * CT;
             pre[u] = i < nsw ? load_scale(i) : 0.0f;
         }
-        if (tid == 0) WS_MARK2(2);
         for (int i = tid; i < kbox * 4 * sast; i += CT)  // tokens the launch does not carry
             if ((i % sast) >= p.m) sa_s[i] = 0.0f;
-        if (tid == 0) WS_MARK2(3);
         const int chunks_per_row = kbox * 16;  // 8-element chunks over the padded K
         const int total = p.mp * chunks_per_row;
         // four chunks per thread and pass: all loads are in flight before the first is used
@@ -297,7 +277,6 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
                 }
             }
         }
-        if (tid == 0) WS_MARK2(4);
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int i = tid + u * CT;
@@ -305,10 +284,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         }
         for (int i = tid + 4 * CT; i < nsw; i += CT) sw_s[sw_index(i)] = load_scale(i);
     }
-    if (tid == 0) WS_MARK2(5);
     consumer_bar_n<CT>();
-    if (tid == 0) WS_MARK2(6);
-    WS_MARK(1);
 
     const int g = lane >> 2, tq = lane & 3;
     const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8;  // ldmatrix source row of this lane
@@ -349,11 +325,10 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     };
     auto run_item = [&](int b0, int nb, int slot, int pad) {
         const int s = rp.s;
-        mbar_wait(full0 + s * 8, rp.ph, X.status);
-        if (item == 0) WS_MARK(4);
+        const bool landed = mbar_wait(full0 + s * 8, rp.ph, X.status);  // false: a wait gave up, the step is void
         const uint32_t sbase = stage0 + s * p.stage_bytes;
         const uint32_t swrow = smem_u32(sw_s) + (uint32_t)(slot * p.skb * 4);
-        for (int bi = wide ? 0 : warp; bi < nb && tg_active; bi += wide ? 1 : CW) {
+        for (int bi = wide ? 0 : warp; bi < nb && tg_active && landed; bi += wide ? 1 : CW) {
             const int box = b0 + bi;
             const uint32_t bbase = sbase + bi * pad * 128 + lm_row * 128;
             const uint32_t sw7 = (uint32_t)((bi * pad + lm_row) & 7);  // 128B-swizzle phase of this row's address
@@ -427,12 +402,11 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     };
     auto run_item_gemv = [&](int b0, int nb, int slot, int pad) {
         const int s = rp.s;
-        mbar_wait(full0 + s * 8, rp.ph, X.status);
-        if (item == 0) WS_MARK(4);
+        const bool landed = mbar_wait(full0 + s * 8, rp.ph, X.status);  // false: a wait gave up, the step is void
         const uint32_t sbase = stage0 + s * p.stage_bytes;
         const uint32_t swrow = smem_u32(sw_s) + (uint32_t)(slot * p.skb * 4);
         const uint32_t xbase = smem_u32(q_s) + (uint32_t)(cch * 32);
-        for (int bi = warp; bi < nb; bi += CW) {
+        for (int bi = warp; bi < nb && landed; bi += CW) {
             const int box = b0 + bi;
             const int kb = box * 4 + (cch >> 1);  // the 32-wide K block of this lane's chunk
             const float sw = kb < kb32 ? lds_f32(swrow + (uint32_t)(((kofs + kb * 32) >> p.bk_shift) * 4)) : 0.0f;
@@ -527,7 +501,6 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
         }
         if (tid < 128 && tok_t < p.m) part_s[tok_t * PR + t * kGroupRows + row_t] = v;
     }
-    WS_MARK(2);
     consumer_bar_n<CT>();  // part_s complete
 
     // Visit every (token, valid row) of this CTA: fn(tok, global row, value index in part_s).
@@ -541,7 +514,6 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
 
     if (solo) {
         for_rows([&](int tok, int row, int pi) { A.out[(size_t)tok * p.n + row] = part_s[pi]; });
-        WS_MARK(5);
         return;
     }
     const uint32_t *myflags = reinterpret_cast<const uint32_t *>(X.sym[X.rank] + p.lay.flags_off) +

@@ -154,7 +154,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
     const uint32_t tempty0 = done0 + kMaxStages * 8;
     const int NB = kUmmaTmemCols / (SL * kUmmaSlabCols);  // TMEM buffers (host keeps SL <= 4, so NB >= 2)
     const uint32_t stage_bytes = (uint32_t)(SL * p.pitch);
-    WS_MARK(0);
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
@@ -248,7 +247,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA
         quant_bar();
-        WS_MARK_T(1, 32);
 
         if (warp == 1) {
             // -------------------------------------------------------- MMA issue (one thread)
@@ -258,11 +256,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
                     for (int s0 = 0; s0 < kslabs; s0 += SL, ++item) {
                         const int nsl = min(SL, kslabs - s0);
                         const int s = item % NS, tb = item % NB;
-                        WS_MARK2(item * 4 + 0);
                         mbar_wait(tempty0 + tb * 8, (((uint32_t)(item / NB)) & 1u) ^ 1u, X.status);
                         mbar_wait(full0 + s * 8, ((uint32_t)(item / NS)) & 1u, X.status);
                         tc_fence_after();
-                        WS_MARK2(item * 4 + 1);
                         for (int j = 0; j < nsl; ++j) {
                             const int slab = s0 + j;
                             const uint32_t a_addr = stage0 + s * stage_bytes + j * p.pitch;
@@ -272,9 +268,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
                                 umma_f8_ss(tmem_base + (tb * SL + j) * kUmmaSlabCols + b * 16,
                                            umma_desc(a_addr + b * 32, 1024), umma_desc(b_addr + b * 32, 0), kUmmaIdesc);
                         }
-                        WS_MARK2(item * 4 + 2);
                         umma_commit(done0 + s * 8);  // stage consumed and its accumulators complete
-                        WS_MARK2(item * 4 + 3);
                     }
                 }
             }
@@ -309,7 +303,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
                     if (j == 0) {
                         mbar_wait(done0 + (item % NS) * 8, ((uint32_t)(item / NS)) & 1u, X.status);
                         tc_fence_after();
-                        if (tid == 64) WS_MARK2(128 + item * 2);
                     }
                     const int nblk = min(4, kb32 - sl * 4);
                     const uint32_t col = tlane + ((item % NB) * SL + j) * kUmmaSlabCols;
@@ -319,7 +312,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
                 };
                 auto loaded_slab = [&](int sl) {  // after the wait: the last slab of a stage frees its TMEM buffer
                     if ((sl % SL) == SL - 1 || sl == kslabs - 1) {
-                        if (tid == 64) WS_MARK2(128 + (item0 + sl / SL) * 2 + 1);
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(tempty0 + ((item0 + sl / SL) % NB) * 8);
@@ -347,7 +339,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
                 issue_slab(0, cur);
                 tmem_ld_wait(cur);
                 loaded_slab(0);
-                if (c == 0) WS_MARK_T(4, 64);
                 for (int slab = 0; slab < kslabs; slab += 2) {
                     // cur holds slab; fetch slab+1 into nxt while adding cur, then the other way round
                     if (slab + 1 < kslabs) issue_slab(slab + 1, nxt);
@@ -364,7 +355,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
                     }
                 }
                 item0 += (kslabs + SL - 1) / SL;
-                WS_MARK_T(2, 64);
                 // publish this chunk's rows
                 if (mine) {
                     if (solo) {
@@ -498,8 +488,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fp8_umma_kernel(const __grid_
         }
     }
 
-    WS_MARK_T(5, 64);
-    WS_MARK_T(3, 64);
     // ---- teardown: every TMEM read and MMA has completed once all threads are here
     tc_fence_before();
     __syncthreads();

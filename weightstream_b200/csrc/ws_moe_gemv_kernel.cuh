@@ -33,7 +33,6 @@
 
 #include "ws_device.cuh"
 #include "ws_moe_kernel.cuh"  // kMoeMaxRoutes, kMoeMaxExperts, e8m0_f32
-#include "ws_fp8_kernel.cuh"  // WS_MARK2 (probe builds only)
 
 namespace ws {
 
@@ -307,7 +306,6 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
     // pass table, activations and the step sequence come from earlier work on the stream
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t seq = step_begin(X);
-    if (tid == 0) WS_MARK2(2);
     const int NP = *reinterpret_cast<const int32_t *>(A.work + W.hdr);
     {
         const uint2 *src = reinterpret_cast<const uint2 *>(A.work + W.pass);
@@ -343,7 +341,7 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
                 const MoePass P = pass_s[ps];
                 for (int j = 0; j < P.nr; ++j, ++xi) {  // the pass's activations, one ring slot per route
                     const int xs = xi % kMoeXSlots;
-                    mbar_wait(xempty0 + xs * 8, (((uint32_t)(xi / kMoeXSlots)) & 1u) ^ 1u, X.status);
+                    if (!mbar_wait(xempty0 + xs * 8, (((uint32_t)(xi / kMoeXSlots)) & 1u) ^ 1u, X.status)) return;
                     if (lane == 0) {
                         const int route = sorted_s[P.first + j];
                         const uint32_t dst = xring0 + xs * S.xbytes;
@@ -359,7 +357,7 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
                 }
                 const int s = rp.s;
                 const int64_t erow = (int64_t)P.expert * p.n + r0;
-                mbar_wait(empty0 + s * 8, rp.ph ^ 1u, X.status);
+                if (!mbar_wait(empty0 + s * 8, rp.ph ^ 1u, X.status)) return;  // a wait gave up: stop streaming
                 const uint32_t sbase = stage0 + s * p.stage_bytes;
                 if (lane == 0) {
                     mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)(rows * (kbytes + kb32)));
@@ -448,7 +446,6 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
                     }
                 }
             };
-            if (tid == 0) WS_MARK2(8 + ps * 4 + 0);
             for (int j = 0; j < P.nr;) {
                 const int rt = P.nr - j >= 2 ? 2 : 1;
                 uint32_t xa[16], xb[16];
@@ -457,10 +454,8 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
                 take_route(j, xa, sa, ta);
                 if (rt == 2) take_route(j + 1, xb, sb2, tb);
                 if (!landed) {
-                    if (tid == 0) WS_MARK2(8 + ps * 4 + 1);
                     mbar_wait(full0 + s * 8, rp.ph, X.status);
                     landed = true;
-                    if (tid == 0) WS_MARK2(8 + ps * 4 + 2);
                 }
                 if (wactive) {
                     if (rt == 2) rows_pass(std::integral_constant<int, 2>{}, xa, xb, sa, sb2, ta, tb);
@@ -470,12 +465,9 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + s * 8);
-            if (tid == 0) WS_MARK2(8 + ps * 4 + 3);
         }
     }
-    if (tid == 0) WS_MARK2(1);
     consumer_bar_n<CT>();  // accumulators complete
-    if (tid == 0) WS_MARK2(3);
 
     // Value of (token, row r of this CTA): the K slices in ascending order.
     auto value = [&](int tok, int r) {

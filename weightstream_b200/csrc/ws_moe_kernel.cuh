@@ -20,7 +20,7 @@
 #include <math.h>
 
 #include "ws_device.cuh"
-#include "ws_fp8_kernel.cuh"  // RowPlan, WS_MARK
+#include "ws_fp8_kernel.cuh"  // RowPlan
 
 namespace ws {
 
@@ -142,7 +142,6 @@ __device__ __forceinline__ void moe_down_body(const MoeParams &p) {
     // routes, hidden states and the step sequence come from earlier work on the stream
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t seq = step_begin(X);
-    if (tid == 0) WS_MARK2(2);
 
     // ---- pass table (every CTA builds the same one): all threads, including the producer
     for (int i = tid; i < A.e_len; i += kThreads) cnt_s[i] = 0;
@@ -203,7 +202,7 @@ __device__ __forceinline__ void moe_down_body(const MoeParams &p) {
             for (int t0 = 0; t0 < ntile; t0 += TPI, ++item) {
                 const int nt = min(TPI, ntile - t0);
                 const int s = item % NS;
-                mbar_wait(empty0 + s * 8, (((uint32_t)(item / NS)) & 1u) ^ 1u, X.status);
+                if (!mbar_wait(empty0 + s * 8, (((uint32_t)(item / NS)) & 1u) ^ 1u, X.status)) return;
                 uint32_t bytes = 0;
                 for (int j = 0; j < nt; ++j) bytes += (uint32_t)(tcnt(t0 + j) * (kbox * 128 + kb32));
                 if (lane == 0) {
@@ -359,18 +358,14 @@ __device__ __forceinline__ void moe_down_body(const MoeParams &p) {
     const bool solo = p.world == 1;
 
     // ---- passes in ascending expert id
-    if (tid == 0) WS_MARK2(0);
     for (int ps = 0; ps < NP; ++ps) {
-        if (tid == 0) WS_MARK2(8 + ps * 4 + 0);
         prep_pass(ps);
-        if (tid == 0) WS_MARK2(8 + ps * 4 + 1);
         const int nr = pass_n[ps];
         for (int t0 = 0; t0 < ntile; t0 += TPI) {
             const int nt = min(TPI, ntile - t0);
 #pragma unroll
             for (int j = 0; j < 2; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
             run_item(nt);
-            if (tid == 0 && t0 == 0) WS_MARK2(8 + ps * 4 + 2);
             const float v = reduce_warps();
             if (tile_t < nt && col_t < nr) {
                 const int tok = pass_r[ps * 8 + col_t] / p.top_k;
@@ -378,7 +373,6 @@ __device__ __forceinline__ void moe_down_body(const MoeParams &p) {
             }
         }
     }
-    if (tid == 0) WS_MARK2(1);
     consumer_bar();  // part_s complete
 
     // Visit every (token, valid row) of this CTA: fn(tok, global row, index in part_s).
