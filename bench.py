@@ -525,6 +525,8 @@ def run_ours(args) -> None:
     peak, peak_src = measured_peak_gbs()
     W = build_workload(args.workload, m, tp, synth, torch, dist, dev, sh, l2_bytes)
     ep = W.ep
+    if args.kernel:
+        ep.set_kernel(args.kernel)
     if world > 1:
         ep.connect_process_group()
 
@@ -659,6 +661,8 @@ def run_ours(args) -> None:
                    "sample": f"{cpu_n} full o_proj steps (M={m}, whole K), single thread as the reference engine runs"}
         else:
             cpu = None
+        if args.kernel:
+            detail["kernel"] = f"ws_tp_set_kernel({args.kernel})"
         detail["timing"] = (("CUDA events around one replay of a CUDA graph holding all K steps (a chain: consecutive steps "
                              "overlap through programmatic dependent launch)" if graphed
                              else "CUDA events around K eager launches") + ", one stream, max over ranks")
@@ -698,6 +702,8 @@ def main() -> None:
     ap.add_argument("--m", type=int, default=1, help="activation rows per step (1 = decode)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a graph replay")
     ap.add_argument("--no-others", action="store_true", help="skip the short measurements of the other fused steps")
+    ap.add_argument("--kernel", type=int, default=0, choices=[0, 1, 2],
+                    help="kernel choice as ws_tp_set_kernel takes it (0 = automatic, the default of the library)")
     ap.add_argument("--workload", default="o_proj", choices=["o_proj", "shared_down", "moe_down", "lm_head"],
                     help="o_proj is the headline step; the others are the path's remaining fused steps")
     args = ap.parse_args()

@@ -518,3 +518,100 @@ def test_routing_weight_is_applied_before_quantisation(dev, tpmod):
         assert torch.isfinite(b).all()
     finally:
         ep.close()
+
+
+# ----------------------------------------------------------------------------- the measured configurations at full size
+def torch_bf16(shape, seed, dev):
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    return torch.randn(shape, generator=g, device=dev).to(torch.bfloat16)
+
+
+def bf16_to_f32_host(t):
+    return (t.view(torch.int16).cpu().numpy().view(np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def test_oproj_full_size_64_rows(dev, tpmod, oracle):
+    """o_proj at the measured size with 64 activation rows: x bf16 [64, 8192], W FP8 [7168, 8192],
+    128x128 fp32 scales, one pass over the weights."""
+    from weightstream_b200 import synth
+    n, k, m = 7168, 8192, 64
+    wd, sd = synth.torch_fp8_weight(n, k, seed=synth.config_seed("o_proj", m, 1), device=dev)
+    x = torch_bf16((m, k), 64, dev)
+    ep = tpmod.Endpoint(max_m=64, max_n=n)
+    try:
+        launches0 = ep.launches
+        out = ep.fp8_rowpar_gemm_allreduce(x, wd, sd)
+        ep.check()
+        assert ep.launches - launches0 <= 2, "64 rows must not loop over the weights"
+        want = oracle.fp8_gemv(wd.cpu().numpy(), sd.cpu().numpy(), bf16_to_f32_host(x), bn=128, bk=128, threads=oracle.max_threads())
+        err = rel_l2(out.cpu().numpy(), want)
+        assert err <= REL_L2_TOL and err < 5e-5, err
+    finally:
+        ep.close()
+
+
+@pytest.mark.parametrize("m", [1, 2])
+def test_lm_head_full_size(dev, tpmod, oracle, m):
+    """lm_head at the measured size, W FP8 [129280, 7168]: logits against the oracle, argmax equal to
+    sample.rs:13-23 on the oracle's logits, and the gap between the two largest logits recorded (a
+    near-tie would make the argmax comparison meaningless)."""
+    from weightstream_b200 import synth
+    vocab, k = 129280, 7168
+    wd, sd = synth.torch_fp8_weight(vocab, k, seed=synth.config_seed("lm_head", m, 1), device=dev)
+    x = torch_bf16((m, k), 65 + m, dev)
+    ep = tpmod.Endpoint(max_m=8, max_n=16, max_vocab=vocab)
+    try:
+        logits, am = ep.lm_head_allgather_argmax(x, wd, sd, vocab_row0=0, vocab=vocab)
+        _, am2 = ep.lm_head_allgather_argmax(x, wd, sd, vocab_row0=0, vocab=vocab, want_logits=False)
+        ep.check()
+        want = oracle.fp8_gemv(wd.cpu().numpy(), sd.cpu().numpy(), bf16_to_f32_host(x), bn=128, bk=128, threads=oracle.max_threads())
+        got = logits.cpu().numpy()
+        err = rel_l2(got, want)
+        assert err <= REL_L2_TOL and err < 5e-5, err
+        top2 = np.sort(want, axis=1)[:, -2:]
+        gap = float((top2[:, 1] - top2[:, 0]).min())
+        assert gap > 1e-3 * float(np.abs(top2).max()), f"seed gives a near-tie (gap {gap}); pick another"
+        for t in range(m):
+            assert int(am[t].item()) == int(am2[t].item()) == oracle.argmax(want[t]) == oracle.argmax(got[t])
+    finally:
+        ep.close()
+
+
+@pytest.mark.parametrize("world", [1, 8])
+def test_moe_full_size_64_tokens(dev, tpmod, oracle, world):
+    """The MoE step at the measured size: 384 experts of MXFP4 [7168, 2048], top-6 of 64 tokens (about
+    246 experts hit, several routes on some), on one rank and as 8 virtual ranks of 48 experts."""
+    from weightstream_b200 import synth
+    E, n, k, top_k, m = 384, 7168, 2048, 6, 64
+    rng = np.random.default_rng(synth.config_seed("moe_full", m, world))
+    ids, rw = synth.routes(rng, m, E, top_k)
+    h = torch_bf16((m * top_k, k), 99, dev)
+    hf = bf16_to_f32_host(h)
+    el = E // world
+    idd, rwd = torch.from_numpy(ids).to(dev), torch.from_numpy(rw).to(dev)
+    grp = tpmod.LocalGroup(world, max_m=64, max_n=n)
+    try:
+        w2s, s2s, e0s, parts = [], [], [], []
+        for r in range(world):
+            w2, s2 = synth.torch_fp4_experts(el, n, k, seed=7000 + r, device=dev)
+            w2s.append(w2); s2s.append(s2); e0s.append(r * el)
+        outs = grp.moe_down_combine_allreduce([h] * world, [idd] * world, [rwd] * world, w2s, s2s, e0s)
+        grp.check()
+        for r in range(world):  # the oracle on the experts this rank's routes hit, remapped onto a compact slab (order kept)
+            e0 = r * el
+            local = np.unique(ids[(ids >= e0) & (ids < e0 + el)]) - e0
+            ids2 = np.full_like(ids, -1)
+            for i, e in enumerate(local):
+                ids2[ids == e + e0] = i
+            w2h = np.stack([w2s[r][e].cpu().numpy() for e in local]) if len(local) else np.zeros((1, n, k // 2), np.uint8)
+            s2h = np.stack([s2s[r][e].cpu().numpy() for e in local]) if len(local) else np.zeros((1, n, k // 32), np.uint8)
+            parts.append(oracle.moe_down_combine(w2h, s2h, 0, hf, ids2, rw, threads=oracle.max_threads()))
+        want = oracle.allreduce_fold(np.stack(parts))
+        got = [o.cpu().numpy() for o in outs]
+        for r in range(1, world):
+            assert np.array_equal(got[0].view(np.uint32), got[r].view(np.uint32)), f"rank {r} differs from rank 0"
+        err = rel_l2(got[0], want)
+        assert err <= REL_L2_TOL and err < 5e-5, err
+    finally:
+        grp.close()

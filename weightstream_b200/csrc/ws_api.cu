@@ -15,7 +15,7 @@
 #include "../../include/ws_tp.h"
 #include "ws_device.cuh"
 #include "ws_fp8_kernel.cuh"
-#include "ws_fp8_umma_kernel.cuh"
+#include "ws_fp8_bs_kernel.cuh"
 #include "ws_misc_kernels.cuh"
 #include "ws_moe_kernel.cuh"
 #include "ws_moe_gemv_kernel.cuh"
@@ -37,7 +37,7 @@ struct ws_tp {
     uint64_t timeout_ns = 0;
     int split = 1;
     int pdl = 1;         // programmatic dependent launch for the FP8 mma.sync kernel
-    int kernel_sel = 0;  // 0: automatic (CUDA cores for 1-2 rows, mma.sync for 3-8), 1: mma.sync, 2: tcgen05 when the shape fits
+    int kernel_sel = 0;  // 0: automatic (CUDA cores for 1-2 rows, block-scaled tcgen05 above), 1: mma.sync, 2: tcgen05 whenever the shape fits
     // host-buffer entry points
     cudaStream_t hstream = nullptr;
     void *pin = nullptr;
@@ -60,6 +60,9 @@ struct ws_tp {
     size_t moe_work_bytes = 0;
     float *moe_acc = nullptr;
     size_t moe_acc_bytes = 0;
+    // block-scaled tcgen05 step: the step's quantised activations [64][k] and their scale atoms
+    uint8_t *bs_work = nullptr;
+    size_t bs_work_bytes = 0;
     std::string err;
 };
 
@@ -262,7 +265,8 @@ ws_status_t ws_tp_create(int32_t world, int32_t rank, int32_t device, const ws_t
     if (world == 1) tp->connected = true;
     if (set_smem(tp, moe_gemv_kernel) != WS_OK || set_smem(tp, fp8_rowpar_kernel<0>) != WS_OK || set_smem(tp, fp8_rowpar_kernel<1>) != WS_OK ||
         set_smem(tp, fp8_rowpar_kernel<2>) != WS_OK || set_smem(tp, moe_down_kernel) != WS_OK ||
-        set_smem(tp, fp8_umma_kernel) != WS_OK)
+        set_smem(tp, fp8_bs_kernel<16>) != WS_OK || set_smem(tp, fp8_bs_kernel<32>) != WS_OK ||
+        set_smem(tp, fp8_bs_kernel<64>) != WS_OK)
         return bail(WS_ERR_CUDA);
     *out = tp;
     return WS_OK;
@@ -281,6 +285,7 @@ ws_status_t ws_tp_destroy(ws_tp_t *tp) {
     if (tp->pin_status) cudaFreeHost(tp->pin_status);
     if (tp->moe_work) cudaFree(tp->moe_work);
     if (tp->moe_acc) cudaFree(tp->moe_acc);
+    if (tp->bs_work) cudaFree(tp->bs_work);
     if (tp->sym) cudaFree(tp->sym);
     if (tp->counters) cudaFree(tp->counters);
     delete tp;
@@ -392,57 +397,84 @@ static ws_status_t validate_fp8(ws_tp *tp, const ws_fp8_gemm_args_t &a, bool lm_
     return WS_OK;
 }
 
-// Plan of the tcgen05 path for one fused step; ok = false when the shape does not fit it.
-struct UmmaPlan {
+// Plan of the block-scaled tcgen05 path for one fused step; ok = false when the shape does not fit it
+// (it needs fp32 weight scales whose K blocks are whole 128-wide slabs, and k a multiple of 128).
+struct BsPlan {
     bool ok;
-    int chunk_rows, nchunk, pitch, slabs_per_stage, nstages, nslot_max;
+    int mp, chunk_rows, nchunk, a_pitch, b_pitch, slabs_per_stage, nstages, nslot_max, nacc;
     size_t smem;
 };
-static UmmaPlan umma_plan(int n, int k, int bn, int skb, int ncta) {
-    UmmaPlan u{};
-    const int kslabs = (k + 127) / 128;
-    const int crmax = (n + ncta - 1) / ncta;
+static BsPlan bs_plan(const ws_fp8_gemm_args_t &a, int mt, int skb, int ncta) {
+    BsPlan u{};
+    if (a.scale_kind != WS_SCALE_F32 || a.block_k % 128 || a.k % 128 || mt > kBsMaxTokens) return u;
+    u.mp = mt <= 16 ? 16 : mt <= 32 ? 32 : 64;
+    const int crmax = (a.n + ncta - 1) / ncta;
     u.nchunk = (crmax + 127) / 128;
     u.chunk_rows = (crmax + u.nchunk - 1) / u.nchunk;
-    u.pitch = (u.chunk_rows + 7) / 8 * 8 * 128;
-    u.slabs_per_stage = std::max(1, std::min(4, kStageBytes / u.pitch));  // <= 4: a stage's accumulators fill at most half of TMEM
-    u.nslot_max = crmax / bn + 2;
-    const UmmaSmem fixed = umma_smem_layout(0, u.slabs_per_stage, u.pitch, kslabs, u.nslot_max, skb);
-    const int stage_bytes = u.slabs_per_stage * u.pitch;
-    int ns = (kSmemBudget - fixed.total - 1024) / stage_bytes;
-    if (ns > kMaxStages) ns = kMaxStages;
+    u.a_pitch = (u.chunk_rows + 7) / 8 * 8 * 128;
+    u.b_pitch = u.mp * 128;
+    const int slab_bytes = u.a_pitch + u.b_pitch + kBsAtomBytes;
+    u.slabs_per_stage = std::max(1, std::min(4, kStageBytes / slab_bytes));
+    u.nslot_max = crmax / a.block_n + 2;
+    u.nacc = std::min((int)kBsMaxAcc, 448 / u.mp);
+    const int fixed = bs_smem_layout(0, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp).total;
+    int ns = (kSmemBudget - fixed - 1024) / (u.slabs_per_stage * slab_bytes);
+    const int kslabs = a.k / 128;
+    const int items = u.nchunk * ((kslabs + u.slabs_per_stage - 1) / u.slabs_per_stage);
+    ns = std::min(ns, std::min((int)kMaxStages, std::max(2, items)));
     u.nstages = ns;
-    u.ok = ns >= 2 && fixed.total < kSmemBudget;
-    if (u.ok) u.smem = (size_t)umma_smem_layout(ns, u.slabs_per_stage, u.pitch, kslabs, u.nslot_max, skb).total + 1024;
+    u.ok = ns >= 2;
+    if (u.ok) u.smem = (size_t)bs_smem_layout(ns, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp).total + 1024;
     return u;
 }
 
-// One fused step over at most 8 activation rows on the tcgen05 path.
-static ws_status_t umma_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t *args, const ws_lm_head_args_t *lm,
-                             int m0, int mt, void *const *streams, int ncta, bool same_device, const UmmaPlan &u,
-                             int skb) {
+static ws_status_t ensure_bs_scratch(ws_tp *tp, size_t bytes) {
+    WS_CUDA(tp, cudaSetDevice(tp->device));
+    if (bytes > tp->bs_work_bytes) {
+        if (tp->bs_work) cudaFree(tp->bs_work);
+        tp->bs_work = nullptr;
+        tp->bs_work_bytes = 0;
+        WS_CUDA(tp, cudaMalloc(&tp->bs_work, bytes));
+        WS_CUDA(tp, cudaMemset(tp->bs_work, 0, bytes));
+        tp->bs_work_bytes = bytes;
+    }
+    return WS_OK;
+}
+
+// A tensor map over a row-major byte matrix with boxes of 128 bytes x box_rows, 128B swizzle (see make_tmap).
+// One fused step over at most 64 activation rows on the block-scaled tcgen05 path: the prep
+// kernel (activation quantisation once per step) followed by the persistent MMA kernel.
+static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t *args, const ws_lm_head_args_t *lm,
+                           int m0, int mt, void *const *streams, int ncta, bool same_device, const BsPlan &u, int skb) {
     ws_tp *t0 = ranks[0];
     const ws_fp8_gemm_args_t &a0 = lm ? lm[0].g : args[0];
-    UmmaParams p{};
-    p.m = mt; p.n = a0.n; p.k = a0.k; p.x_dtype = a0.x_dtype; p.scale_kind = a0.scale_kind;
-    p.bn = a0.block_n; p.bk = a0.block_k; p.world = t0->world;
-    for (p.bk_shift = 0; (1 << p.bk_shift) < p.bk; ++p.bk_shift) {}
-    for (p.bn_shift = 0; (1 << p.bn_shift) < p.bn; ++p.bn_shift) {}
+    BsParams p{};
+    p.m = mt; p.mp = u.mp; p.n = a0.n; p.k = a0.k; p.world = t0->world;
+    for (p.bk_shift = 0; (1 << p.bk_shift) < a0.block_k; ++p.bk_shift) {}
+    for (p.bn_shift = 0; (1 << p.bn_shift) < a0.block_n; ++p.bn_shift) {}
     p.mode = lm ? kModeLmHead : kModeAllReduce;
     p.vocab = lm ? lm[0].vocab : 0;
-    p.chunk_rows = u.chunk_rows; p.nchunk = u.nchunk; p.pitch = u.pitch;
-    p.slabs_per_stage = u.slabs_per_stage; p.nstages = u.nstages; p.nslot_max = u.nslot_max; p.skb = skb;
+    p.chunk_rows = u.chunk_rows; p.nchunk = u.nchunk; p.a_pitch = u.a_pitch; p.b_pitch = u.b_pitch;
+    p.slabs_per_stage = u.slabs_per_stage; p.nstages = u.nstages; p.nslot_max = u.nslot_max; p.skb = skb; p.nacc = u.nacc;
+    // a shard that fits L2 comfortably is asked for in full at kernel start, so that HBM keeps
+    // streaming while the predecessor on the stream finishes and this kernel sets up
+    p.l2_prefetch = (size_t)a0.n * a0.k <= ((size_t)64 << 20) ? 1 : 0;
     p.timeout_ns = t0->timeout_ns;
     p.lay = t0->lay;
+    ActPrepParams q{};
+    q.m = mt; q.mp = u.mp; q.k = a0.k; q.x_dtype = a0.x_dtype;
+    const size_t xq_bytes = (size_t)kBsMaxTokens * a0.k, sf_bytes = (size_t)(a0.k / 128) * kBsAtomBytes;
     for (int i = 0; i < n; ++i) {
         ws_tp *t = ranks[i];
         const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
         if (lm && lm[i].logits) p.gather_logits = 1;
-        ws_status_t s = make_tmap(t, &p.tmap[i], a.w, (uint64_t)a.n, (uint64_t)a.k, (uint64_t)a.ldw, (uint32_t)u.chunk_rows);
+        ws_status_t s = ensure_bs_scratch(t, xq_bytes + sf_bytes);
+        if (s == WS_OK) s = make_tmap(t, &p.tmap_w[i], a.w, (uint64_t)a.n, (uint64_t)a.k, (uint64_t)a.ldw, (uint32_t)u.chunk_rows);
+        if (s == WS_OK) s = make_tmap(t, &p.tmap_x[i], t->bs_work, (uint64_t)u.mp, (uint64_t)a.k, (uint64_t)a.k, (uint32_t)u.mp);
         if (s != WS_OK) { t0->err = t->err; return s; }
         Fp8RankArgs &r = p.r[i];
         const size_t xes = a.x_dtype == WS_ACT_BF16 ? 2 : 4;
-        r.x = static_cast<const char *>(a.x) + (size_t)m0 * a.ldx * xes;
+        r.x = nullptr;
         r.scales = a.scales;
         r.out = lm ? nullptr : a.out + (size_t)m0 * a.n;
         r.logits = lm && lm[i].logits ? lm[i].logits + (size_t)m0 * lm[i].vocab : nullptr;
@@ -450,29 +482,59 @@ static ws_status_t umma_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_
         r.ldx = a.ldx; r.scale_ld = a.scale_ld; r.row0 = a.row0; r.k0 = a.k0;
         r.vocab_row0 = lm ? lm[i].vocab_row0 : 0;
         r.ctx = make_ctx(t);
+        p.sfb[i] = t->bs_work + xq_bytes;
+        p.w[i] = a.w;
+        p.ldw[i] = a.ldw;
+        q.r[i].x = static_cast<const char *>(a.x) + (size_t)m0 * a.ldx * xes;
+        q.r[i].xq = t->bs_work;
+        q.r[i].sfb = t->bs_work + xq_bytes;
+        q.r[i].ldx = a.ldx;
     }
     for (int i = 0; i < n; ++i) ranks[i]->step++;
+    void (*const kernel)(BsParams) = u.mp == 16 ? fp8_bs_kernel<16> : u.mp == 32 ? fp8_bs_kernel<32> : fp8_bs_kernel<64>;
+    const int prep_blocks = (int)(((int64_t)u.mp * (a0.k / 8) + 255) / 256);
     if (same_device) {
         WS_CUDA(t0, cudaSetDevice(t0->device));
-        return launch(t0, fp8_umma_kernel, p, ncta, n, kUmmaThreads, u.smem, static_cast<cudaStream_t>(streams ? streams[0] : nullptr));
+        cudaStream_t cs = static_cast<cudaStream_t>(streams ? streams[0] : nullptr);
+        ws_status_t s = launch(t0, act_prep_kernel, q, prep_blocks, n, 256, 0, cs, t0->pdl != 0, false);
+        if (s != WS_OK) return s;
+        return launch(t0, kernel, p, ncta, n, kBsThreads, u.smem, cs, t0->pdl != 0);
     }
     for (int i = 0; i < n; ++i) {
-        UmmaParams q = p;
-        q.r[0] = p.r[i];
-        q.tmap[0] = p.tmap[i];
+        BsParams pi = p;
+        pi.r[0] = p.r[i];
+        pi.tmap_w[0] = p.tmap_w[i];
+        pi.tmap_x[0] = p.tmap_x[i];
+        pi.sfb[0] = p.sfb[i];
+        pi.w[0] = p.w[i];
+        pi.ldw[0] = p.ldw[i];
+        ActPrepParams qi = q;
+        qi.r[0] = q.r[i];
         WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
-        ws_status_t s = launch(ranks[i], fp8_umma_kernel, q, ncta, 1, kUmmaThreads, u.smem,
-                               static_cast<cudaStream_t>(streams ? streams[i] : nullptr));
+        cudaStream_t cs = static_cast<cudaStream_t>(streams ? streams[i] : nullptr);
+        ws_status_t s = launch(ranks[i], act_prep_kernel, qi, prep_blocks, 1, 256, 0, cs, t0->pdl != 0, false);
+        if (s == WS_OK) s = launch(ranks[i], kernel, pi, ncta, 1, kBsThreads, u.smem, cs, t0->pdl != 0);
         if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
     }
     return WS_OK;
+}
+
+// Whether rows [.., +mt) of this step go to the block-scaled tcgen05 path: always when the caller
+// selected it, by default from three rows up (one and two rows run on CUDA cores).
+static bool bs_wanted(const ws_tp *t0, int mt) {
+    return t0->kernel_sel == 2 || (t0->kernel_sel == 0 && mt >= 3);
 }
 
 // Activation rows the next launch takes: up to 64 when their quantised copies fit in shared
 // memory beside at least three weight stages (the weights are then streamed once for all of
 // them), else 8.
 static int fp8_rows_per_launch(const ws_tp *t0, const ws_fp8_gemm_args_t &a, int ncta, int rem) {
-    if (rem <= 8 || t0->kernel_sel == 2) return std::min(rem, 8);
+    {   // the tensor-memory path streams the weights once for up to 64 rows
+        const int mt = std::min(rem, (int)kBsMaxTokens);
+        const int skb = (int)((a.k0 + a.k - 1) / a.block_k - a.k0 / a.block_k + 1);
+        if (bs_wanted(t0, mt) && bs_plan(a, mt, skb, ncta).ok) return mt;
+    }
+    if (rem <= 8) return rem;
     const int kbox = (a.k + 127) / 128;
     const int Gm = a.n / kGroupRows / ncta;
     const int skb = (int)((a.k0 + a.k - 1) / a.block_k - a.k0 / a.block_k + 1);
@@ -489,14 +551,14 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
                             int m0, int mt, void *const *streams, int ncta, bool same_device) {
     ws_tp *t0 = ranks[0];
     const ws_fp8_gemm_args_t &a0 = lm ? lm[0].g : args[0];
-    if (t0->kernel_sel == 2) {  // tensor-memory path whenever the shape fits it
+    if (bs_wanted(t0, mt)) {  // tensor-memory path whenever the shape fits it
         int64_t skb_u = 1;
         for (int i = 0; i < n; ++i) {
             const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
             skb_u = std::max<int64_t>(skb_u, (a.k0 + a.k - 1) / a.block_k - a.k0 / a.block_k + 1);
         }
-        const UmmaPlan u = umma_plan(a0.n, a0.k, a0.block_n, (int)skb_u, ncta);
-        if (u.ok) return umma_step(ranks, n, args, lm, m0, mt, streams, ncta, same_device, u, (int)skb_u);
+        const BsPlan u = bs_plan(a0, mt, (int)skb_u, ncta);
+        if (u.ok) return bs_step(ranks, n, args, lm, m0, mt, streams, ncta, same_device, u, (int)skb_u);
     }
     Fp8Params p{};
     p.m = mt; p.n = a0.n; p.k = a0.k; p.x_dtype = a0.x_dtype; p.scale_kind = a0.scale_kind;
@@ -553,7 +615,11 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
         r.ldx = a.ldx; r.scale_ld = a.scale_ld; r.row0 = a.row0; r.k0 = a.k0;
         r.vocab_row0 = lm ? lm[i].vocab_row0 : 0;
         r.ctx = make_ctx(t);
+        p.w[i] = a.w;
+        p.ldw[i] = a.ldw;
     }
+    // a shard that fits L2 comfortably is asked for in full once the stage ring is primed
+    p.l2_prefetch = (size_t)p.n * p.k <= ((size_t)64 << 20) ? 1 : 0;
     // every endpoint advances by one step
     for (int i = 0; i < n; ++i) ranks[i]->step++;
     if (same_device) {
@@ -565,6 +631,8 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
         q.r[0] = p.r[i];
         q.tmap[0][0] = p.tmap[i][0];
         q.tmap[0][1] = p.tmap[i][1];
+        q.w[0] = p.w[i];
+        q.ldw[0] = p.ldw[i];
         WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
         ws_status_t s = launch(ranks[i], kernel, q, ncta, 1, fp8_threads(gt), smem,
                                static_cast<cudaStream_t>(streams ? streams[i] : nullptr), t0->pdl != 0);
@@ -659,6 +727,7 @@ static ws_status_t ensure_moe_scratch(ws_tp *tp, size_t work_bytes, size_t acc_b
     }
     if (acc_bytes > tp->moe_acc_bytes) {
         if (tp->moe_acc) cudaFree(tp->moe_acc);
+    if (tp->bs_work) cudaFree(tp->bs_work);
         tp->moe_acc = nullptr;
         tp->moe_acc_bytes = 0;
         WS_CUDA(tp, cudaMalloc(&tp->moe_acc, acc_bytes));
@@ -1064,7 +1133,7 @@ ws_status_t ws_act_quant_fp8(const void *x, int64_t ldx, int32_t x_dtype, int32_
     return cudaGetLastError() == cudaSuccess ? WS_OK : WS_ERR_CUDA;
 }
 
-// 0 (default): automatic; 1: the mma.sync kernel; 2: the tcgen05 kernel when the shape fits.
+// 0 (default): automatic; 1: the mma.sync kernel; 2: the block-scaled tcgen05 kernel when the shape fits.
 ws_status_t ws_tp_set_kernel(ws_tp_t *tp, int32_t which) {
     if (!tp || which < 0 || which > 2) return WS_ERR_INVALID;
     tp->kernel_sel = which;

@@ -53,10 +53,15 @@ struct alignas(64) Fp8Params {
     int32_t gather_logits, ragged;   // ragged = 0: leftover tiles go whole to the first CTAs
     int32_t bk_shift, bn_shift;      // log2 of the scale block edges
     int32_t part_rows, gran;         // partial rows reserved per token; row granularity (1,2,4,8) of the ragged share
-    int32_t stage_bytes, pad1;       // bytes of one weight stage: a whole number of 2 KB boxes (fp8_stage_boxes)
+    int32_t stage_bytes, l2_prefetch;  // bytes of one weight stage: a whole number of 2 KB boxes (fp8_stage_boxes); see below
     uint64_t timeout_ns;
     SymLayout lay;
     Fp8RankArgs r[WS_MAX_WORLD];
+    // l2_prefetch: once the stage ring is full for the first time, the producer asks L2 for the rest
+    // of this CTA's rows (weights are static), so that HBM keeps streaming while the predecessor on
+    // the stream finishes and this kernel quantises its activations.  Needs the plain addresses:
+    const uint8_t *w[WS_MAX_WORLD];
+    int64_t ldw[WS_MAX_WORLD];
 };
 
 // Consumer warps per CTA.  Sixteen warps instead of eight changed neither formulation's time by
@@ -175,6 +180,15 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
     if (warp == CW) {
         // ------------------------------------------------------------ TMA producer warp
         RingPos rp;
+        int issued = 0;
+        bool prefetched = !p.l2_prefetch;
+        auto prefetch_rest = [&]() {  // every row of this CTA after its first tile, one request per row
+            for (int t = 1; t < ntile; ++t)
+                for (int r = lane; r < tcnt(t); r += 32)
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;"
+                                 ::"l"(p.w[vr] + (size_t)(trow(t) + r) * (size_t)p.ldw[vr]), "r"((uint32_t)(p.k & ~15)) : "memory");
+            prefetched = true;
+        };
         for (int t = 0; t < ntile; ++t) {
             const int r0 = trow(t), cnt = tcnt(t);
             const int pad = tpad(cnt), cols = p.stage_bytes / (pad * 128);  // box columns one stage holds
@@ -194,8 +208,10 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
                     }
                 }
                 rp.next(NS);
+                if (!prefetched && ++issued >= NS) prefetch_rest();
             }
         }
+        if (!prefetched) prefetch_rest();
         return;
     }
 
