@@ -265,8 +265,8 @@ ws_status_t ws_tp_create(int32_t world, int32_t rank, int32_t device, const ws_t
     if (world == 1) tp->connected = true;
     if (set_smem(tp, moe_gemv_kernel) != WS_OK || set_smem(tp, fp8_rowpar_kernel<0>) != WS_OK || set_smem(tp, fp8_rowpar_kernel<1>) != WS_OK ||
         set_smem(tp, fp8_rowpar_kernel<2>) != WS_OK || set_smem(tp, moe_down_kernel) != WS_OK ||
-        set_smem(tp, fp8_bs_kernel<16>) != WS_OK || set_smem(tp, fp8_bs_kernel<32>) != WS_OK ||
-        set_smem(tp, fp8_bs_kernel<64>) != WS_OK)
+        set_smem(tp, fp8_bs_kernel<16, true>) != WS_OK || set_smem(tp, fp8_bs_kernel<16, false>) != WS_OK ||
+        set_smem(tp, fp8_bs_kernel<32, false>) != WS_OK || set_smem(tp, fp8_bs_kernel<64, false>) != WS_OK)
         return bail(WS_ERR_CUDA);
     *out = tp;
     return WS_OK;
@@ -401,30 +401,42 @@ static ws_status_t validate_fp8(ws_tp *tp, const ws_fp8_gemm_args_t &a, bool lm_
 // (it needs fp32 weight scales whose K blocks are whole 128-wide slabs, and k a multiple of 128).
 struct BsPlan {
     bool ok;
-    int mp, chunk_rows, nchunk, a_pitch, b_pitch, slabs_per_stage, nstages, nslot_max, nacc;
+    int mp, tile_rows, ntiles, a_pitch, b_pitch, slabs_per_stage, nstages, nslot_max, nacc;
+    int fused;  // 1: at most 8 rows, quantised inside the kernel and kept in shared memory for the whole K (no prep kernel)
     size_t smem;
 };
 static BsPlan bs_plan(const ws_fp8_gemm_args_t &a, int mt, int skb, int ncta) {
     BsPlan u{};
     if (a.scale_kind != WS_SCALE_F32 || a.block_k % 128 || a.k % 128 || mt > kBsMaxTokens) return u;
     u.mp = mt <= 16 ? 16 : mt <= 32 ? 32 : 64;
+    // tiles of equal height that deal out evenly: a CTA's share of the rows, cut into as few pieces
+    // of at most 128 rows as possible
     const int crmax = (a.n + ncta - 1) / ncta;
-    u.nchunk = (crmax + 127) / 128;
-    u.chunk_rows = (crmax + u.nchunk - 1) / u.nchunk;
-    u.a_pitch = (u.chunk_rows + 7) / 8 * 8 * 128;
+    const int pieces = (crmax + kBsMmaRows - 1) / kBsMmaRows;
+    u.tile_rows = (crmax + pieces - 1) / pieces;
+    u.ntiles = (a.n + u.tile_rows - 1) / u.tile_rows;
+    const int tiles_per_cta = (u.ntiles + ncta - 1) / ncta;
+    u.a_pitch = (u.tile_rows + 7) / 8 * 8 * 128;
     u.b_pitch = u.mp * 128;
-    const int slab_bytes = u.a_pitch + u.b_pitch + kBsAtomBytes;
-    u.slabs_per_stage = std::max(1, std::min(4, kStageBytes / slab_bytes));
-    u.nslot_max = crmax / a.block_n + 2;
-    u.nacc = std::min((int)kBsMaxAcc, 448 / u.mp);
-    const int fixed = bs_smem_layout(0, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp).total;
-    int ns = (kSmemBudget - fixed - 1024) / (u.slabs_per_stage * slab_bytes);
     const int kslabs = a.k / 128;
-    const int items = u.nchunk * ((kslabs + u.slabs_per_stage - 1) / u.slabs_per_stage);
+    u.fused = mt <= kBsFusedTokens ? 1 : 0;
+    const int slab_bytes = u.fused ? u.a_pitch : u.a_pitch + u.b_pitch + kBsAtomBytes;
+    // slabs per stage: one MMA commit (a ~160 ns stall of the issuing thread) per stage, so several
+    // slabs share it; bounded by the stage size and by tensor memory (each slab has its own
+    // accumulator buffer: groups x slabs x (mp + 4) + 8 columns of 512, at least two groups)
+    u.slabs_per_stage = std::max(1, std::min({4, (56 * 1024) / slab_bytes, 504 / (2 * (u.mp + 4)), kslabs}));
+    u.nslot_max = (tiles_per_cta * u.tile_rows) / a.block_n + 2;
+    u.nacc = std::min((int)kBsMaxAcc, 504 / (u.slabs_per_stage * (u.mp + 4)));
+    const int fixed = bs_smem_layout(0, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp, u.fused ? kslabs : 0).total;
+    int ns = (kSmemBudget - fixed - 1024 - kBsMmaRows * 128) / (u.slabs_per_stage * slab_bytes);
+    const int items = tiles_per_cta * ((kslabs + u.slabs_per_stage - 1) / u.slabs_per_stage);
     ns = std::min(ns, std::min((int)kMaxStages, std::max(2, items)));
     u.nstages = ns;
+    // the epilogue and the producer wait on the same per-stage barrier: the MMA thread must not get a
+    // whole lap of the stage ring ahead of the epilogue, which holds when groups <= stages
+    u.nacc = std::max(1, std::min(u.nacc, ns));
     u.ok = ns >= 2;
-    if (u.ok) u.smem = (size_t)bs_smem_layout(ns, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp).total + 1024;
+    if (u.ok) u.smem = (size_t)bs_smem_layout(ns, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp, u.fused ? kslabs : 0).total + 1024;
     return u;
 }
 
@@ -454,27 +466,28 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
     for (p.bn_shift = 0; (1 << p.bn_shift) < a0.block_n; ++p.bn_shift) {}
     p.mode = lm ? kModeLmHead : kModeAllReduce;
     p.vocab = lm ? lm[0].vocab : 0;
-    p.chunk_rows = u.chunk_rows; p.nchunk = u.nchunk; p.a_pitch = u.a_pitch; p.b_pitch = u.b_pitch;
+    p.tile_rows = u.tile_rows; p.ntiles = u.ntiles; p.a_pitch = u.a_pitch; p.b_pitch = u.b_pitch;
     p.slabs_per_stage = u.slabs_per_stage; p.nstages = u.nstages; p.nslot_max = u.nslot_max; p.skb = skb; p.nacc = u.nacc;
-    // a shard that fits L2 comfortably is asked for in full at kernel start, so that HBM keeps
-    // streaming while the predecessor on the stream finishes and this kernel sets up
-    p.l2_prefetch = (size_t)a0.n * a0.k <= ((size_t)64 << 20) ? 1 : 0;
+    p.x_dtype = a0.x_dtype;
     p.timeout_ns = t0->timeout_ns;
     p.lay = t0->lay;
     ActPrepParams q{};
     q.m = mt; q.mp = u.mp; q.k = a0.k; q.x_dtype = a0.x_dtype;
-    const size_t xq_bytes = (size_t)kBsMaxTokens * a0.k, sf_bytes = (size_t)(a0.k / 128) * kBsAtomBytes;
+    // scratch of one endpoint: quantised activations and their scale atoms
+    const size_t xq_bytes = align_up((int64_t)kBsMaxTokens * a0.k, 256), sf_bytes = (size_t)(a0.k / 128) * kBsAtomBytes;
+
     for (int i = 0; i < n; ++i) {
         ws_tp *t = ranks[i];
         const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
         if (lm && lm[i].logits) p.gather_logits = 1;
-        ws_status_t s = ensure_bs_scratch(t, xq_bytes + sf_bytes);
-        if (s == WS_OK) s = make_tmap(t, &p.tmap_w[i], a.w, (uint64_t)a.n, (uint64_t)a.k, (uint64_t)a.ldw, (uint32_t)u.chunk_rows);
-        if (s == WS_OK) s = make_tmap(t, &p.tmap_x[i], t->bs_work, (uint64_t)u.mp, (uint64_t)a.k, (uint64_t)a.k, (uint32_t)u.mp);
+        ws_status_t s = u.fused ? WS_OK : ensure_bs_scratch(t, xq_bytes + sf_bytes);
+        if (s == WS_OK) s = make_tmap(t, &p.tmap_w[i], a.w, (uint64_t)a.n, (uint64_t)a.k, (uint64_t)a.ldw, (uint32_t)u.tile_rows);
+        uint8_t *const xq = t->bs_work;
+        if (s == WS_OK && !u.fused) s = make_tmap(t, &p.tmap_x[i], xq, (uint64_t)u.mp, (uint64_t)a.k, (uint64_t)a.k, (uint32_t)u.mp);
         if (s != WS_OK) { t0->err = t->err; return s; }
         Fp8RankArgs &r = p.r[i];
         const size_t xes = a.x_dtype == WS_ACT_BF16 ? 2 : 4;
-        r.x = nullptr;
+        r.x = static_cast<const char *>(a.x) + (size_t)m0 * a.ldx * xes;  // read by the fused form only
         r.scales = a.scales;
         r.out = lm ? nullptr : a.out + (size_t)m0 * a.n;
         r.logits = lm && lm[i].logits ? lm[i].logits + (size_t)m0 * lm[i].vocab : nullptr;
@@ -482,21 +495,22 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
         r.ldx = a.ldx; r.scale_ld = a.scale_ld; r.row0 = a.row0; r.k0 = a.k0;
         r.vocab_row0 = lm ? lm[i].vocab_row0 : 0;
         r.ctx = make_ctx(t);
-        p.sfb[i] = t->bs_work + xq_bytes;
-        p.w[i] = a.w;
-        p.ldw[i] = a.ldw;
+        p.sfb[i] = xq + xq_bytes;
         q.r[i].x = static_cast<const char *>(a.x) + (size_t)m0 * a.ldx * xes;
-        q.r[i].xq = t->bs_work;
-        q.r[i].sfb = t->bs_work + xq_bytes;
+        q.r[i].xq = xq;
+        q.r[i].sfb = xq + xq_bytes;
         q.r[i].ldx = a.ldx;
     }
     for (int i = 0; i < n; ++i) ranks[i]->step++;
-    void (*const kernel)(BsParams) = u.mp == 16 ? fp8_bs_kernel<16> : u.mp == 32 ? fp8_bs_kernel<32> : fp8_bs_kernel<64>;
+    void (*const kernel)(BsParams) = u.fused ? fp8_bs_kernel<16, true>
+                                     : u.mp == 16 ? fp8_bs_kernel<16, false>
+                                     : u.mp == 32 ? fp8_bs_kernel<32, false>
+                                                  : fp8_bs_kernel<64, false>;
     const int prep_blocks = (int)(((int64_t)u.mp * (a0.k / 8) + 255) / 256);
     if (same_device) {
         WS_CUDA(t0, cudaSetDevice(t0->device));
         cudaStream_t cs = static_cast<cudaStream_t>(streams ? streams[0] : nullptr);
-        ws_status_t s = launch(t0, act_prep_kernel, q, prep_blocks, n, 256, 0, cs, t0->pdl != 0, false);
+        ws_status_t s = u.fused ? WS_OK : launch(t0, act_prep_kernel, q, prep_blocks, n, 256, 0, cs, t0->pdl != 0, false);
         if (s != WS_OK) return s;
         return launch(t0, kernel, p, ncta, n, kBsThreads, u.smem, cs, t0->pdl != 0);
     }
@@ -506,13 +520,11 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
         pi.tmap_w[0] = p.tmap_w[i];
         pi.tmap_x[0] = p.tmap_x[i];
         pi.sfb[0] = p.sfb[i];
-        pi.w[0] = p.w[i];
-        pi.ldw[0] = p.ldw[i];
         ActPrepParams qi = q;
         qi.r[0] = q.r[i];
         WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
         cudaStream_t cs = static_cast<cudaStream_t>(streams ? streams[i] : nullptr);
-        ws_status_t s = launch(ranks[i], act_prep_kernel, qi, prep_blocks, 1, 256, 0, cs, t0->pdl != 0, false);
+        ws_status_t s = u.fused ? WS_OK : launch(ranks[i], act_prep_kernel, qi, prep_blocks, 1, 256, 0, cs, t0->pdl != 0, false);
         if (s == WS_OK) s = launch(ranks[i], kernel, pi, ncta, 1, kBsThreads, u.smem, cs, t0->pdl != 0);
         if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
     }
@@ -618,8 +630,8 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
         p.w[i] = a.w;
         p.ldw[i] = a.ldw;
     }
-    // a shard that fits L2 comfortably is asked for in full once the stage ring is primed
-    p.l2_prefetch = (size_t)p.n * p.k <= ((size_t)64 << 20) ? 1 : 0;
+    // as in the tensor-memory path: only when a second CTA can be resident beside the predecessor's
+    p.l2_prefetch = (2 * smem <= (size_t)227 * 1024 && (size_t)p.n * p.k <= ((size_t)64 << 20)) ? 1 : 0;
     // every endpoint advances by one step
     for (int i = 0; i < n; ++i) ranks[i]->step++;
     if (same_device) {

@@ -9,22 +9,27 @@
 //                     per-32 UE8M0 exponents in the layout the MMA's scale operand wants (one 512-byte
 //                     atom per 128-wide K slab: byte (t & 31) * 16 + (t >> 5) * 4 + j holds the exponent
 //                     of token t, K block 4 * slab + j).  Both stay in L2 for the main kernel.
-//   fp8_bs_kernel     persistent, one CTA per SM.  A CTA owns a contiguous range of output rows,
-//                     walked in chunks of at most 128 rows = the M of one MMA tile, and streams their
-//                     weights over the whole local K, so every output is a complete dot product
-//                     inside one CTA.  Per 128-byte K slab the producer warp lands, in one stage of a
-//                     shared-memory ring: the weight rows (TMA box, 128B swizzle), the quantised
-//                     activations of all tokens (TMA box from the prep kernel's buffer) and their
-//                     scale atom (bulk copy).  One thread copies the atom into tensor memory
-//                     (tcgen05.cp) and issues four MMAs (M=128, N=tokens, K=32): the activations'
-//                     per-32 scales ride the MMA's scale operand, the weight operand's scale is 2^0,
-//                     and the four K blocks accumulate in tensor memory.  The weights' own scales are
-//                     fp32 per (block_n x block_k) block, which no MMA scale format can carry, so
-//                     four epilogue warps read each slab's accumulators back (tcgen05.ld) and add
-//                     them, times the fp32 weight scale, to their registers while the next slabs'
-//                     MMAs run into the other accumulator buffers.
+//   fp8_bs_kernel     persistent, one CTA per SM.  The rows are cut into tiles of at most 128 rows (the
+//                     M of the MMA) that deal out evenly, and a CTA streams the weights of its tiles over
+//                     the whole local K, so every output is a complete dot product inside one CTA.  Per
+//                     128-byte K slab the producer warp lands, in one stage of a shared-memory ring: the
+//                     tile's weight rows (TMA box, 128B swizzle), the quantised activations of all
+//                     tokens (TMA box from the prep kernel's buffer) and their scale atom (bulk copy).
+//                     One thread copies the atom into tensor memory (tcgen05.cp) and issues four MMAs
+//                     (M=128, N=tokens, K=32): the activations' per-32 scales ride the MMA's scale
+//                     operand, the weight operand's scale is 2^0, and the four K blocks accumulate in
+//                     tensor memory.  The weights' own scales are fp32 per (block_n x block_k) block,
+//                     which no MMA scale format can carry, so every slab gets its own accumulator
+//                     buffer and four epilogue warps read a stage's buffers back (tcgen05.ld) and add
+//                     them, times the fp32 weight scale, to their registers while the next stages'
+//                     MMAs run into the other buffers.
 //
-// Rows past a chunk's end are computed on whatever follows in shared memory and never read back.
+// Measured on B200 and kept in mind above: the tensor pipe needs 30-45 ns per K=32 MMA at M=128 however
+// few of the rows are real (M=64 is not available with block scaling); a tcgen05.commit stalls the
+// issuing thread for ~160 ns; handing partial sums from one CTA to another through L2 (a split of K
+// across CTAs) costs 3-5 us, more than it saves on these shapes.
+//
+// MMA rows past a tile's end are computed on whatever follows in shared memory and never read back.
 // Exchange and lm_head mode are those of the decode kernel (ws_fp8_kernel.cuh): tagged 64-bit
 // words stored into every peer's slots and folded in rank order, or gather + argmax candidates.
 #pragma once
@@ -36,11 +41,15 @@
 
 namespace ws {
 
-constexpr int kBsThreads = 192;      // warp 0: producer, warp 1: MMA issue + TMEM owner, warps 2-5: epilogue
+constexpr int kBsThreads = 224;      // warp 0: producer, warps 1 and 6: MMA issue (warp 1 owns TMEM), warps 2-5: epilogue
 constexpr int kBsTmemCols = 512;
-constexpr int kBsMaxAcc = 8;         // accumulator buffers in tensor memory
+constexpr int kBsMaxAcc = 8;         // accumulator groups in tensor memory (a group = one stage's slabs)
 constexpr int kBsMaxTokens = 64;     // activation rows one launch takes
 constexpr int kBsAtomBytes = 512;    // one scale atom: 128 rows x 4 K blocks
+constexpr int kBsMmaRows = 128;      // M of the MMA; a tile of output rows holds at most as many
+constexpr int kBsFusedTokens = 8;    // most activation rows the fused form (no prep kernel) takes
+constexpr int kBsFusedBBytes = 1024; // fused form, per K slab: 8 token rows x 128 bytes (MMA columns 8-15 re-read them)
+constexpr int kBsFusedAtomBytes = 128;  // fused form, per K slab: the 8 tokens' rows of the scale atom
 
 // ---------------------------------------------------------------- activation prep
 struct ActPrepRank {
@@ -84,39 +93,42 @@ __global__ void __launch_bounds__(256) act_prep_kernel(const __grid_constant__ A
 
 // ---------------------------------------------------------------- main kernel
 struct alignas(64) BsParams {
-    CUtensorMap tmap_w[WS_MAX_WORLD];  // weight shard [n][k bytes], box 128 bytes x chunk_rows, 128B swizzle
+    CUtensorMap tmap_w[WS_MAX_WORLD];  // weight shard [n][k bytes], box 128 bytes x tile_rows, 128B swizzle
     CUtensorMap tmap_x[WS_MAX_WORLD];  // quantised activations [mp][k bytes], box 128 bytes x mp, 128B swizzle
     int32_t m, mp, n, k, bn_shift, bk_shift;
     int32_t world, mode, vocab, gather_logits;
-    int32_t chunk_rows, nchunk;        // rows per chunk (<= 128) and chunks per CTA
+    int32_t x_dtype, pad0;             // fused form only: element type of r[].x
+    int32_t tile_rows, ntiles;         // output rows per tile (<= 128) and tiles of the shard
     int32_t slabs_per_stage, nstages;
     int32_t a_pitch, b_pitch;          // bytes one slab's weights / activations occupy in a stage (multiples of 1024)
-    int32_t skb, nslot_max, nacc, l2_prefetch;
+    int32_t skb, nslot_max, nacc;
     uint64_t timeout_ns;
     SymLayout lay;
-    Fp8RankArgs r[WS_MAX_WORLD];       // x is unused here; scales/out/logits/argmax/row0/k0/ctx as in the decode kernel
+    Fp8RankArgs r[WS_MAX_WORLD];       // x: fused form only; scales/out/logits/argmax/row0/k0/ctx as in the decode kernel
     const uint8_t *sfb[WS_MAX_WORLD];  // the prep kernel's scale atoms
-    const uint8_t *w[WS_MAX_WORLD];    // weight shard base and row stride (L2 prefetch only; the data path uses tmap_w)
-    int64_t ldw[WS_MAX_WORLD];
 };
 
 struct BsSmem {
     int32_t a, b, sf, sfa, sw, cand, bars, misc, total;
 };
+// fused_kslabs = 0: activations and their scale atoms travel through the stages (prep-kernel form).
+// fused_kslabs = k / 128: the kernel quantises its (at most 8) activation rows itself and keeps them
+// for the whole K: 8 rows x 128 bytes and a 128-byte scale atom per slab; the stages hold weights only.
 __host__ __device__ inline BsSmem bs_smem_layout(int nstages, int slabs_per_stage, int a_pitch, int b_pitch, int nslot_max,
-                                                 int skb, int mp) {
+                                                 int skb, int mp, int fused_kslabs) {
     BsSmem s{};
     const int nsl = nstages * slabs_per_stage;
+    const int b_bytes = fused_kslabs ? fused_kslabs * kBsFusedBBytes : nsl * b_pitch;
     int o = 0;
     s.a = o;    o += nsl * a_pitch;
-    s.b = o;    o += nsl * b_pitch;
-    // an MMA reads 128 rows of its weight slab whatever the chunk holds: keep 16 KB readable behind the last one
-    if (nsl * b_pitch < 16384) o += 16384 - nsl * b_pitch;
-    s.sf = o;   o += nsl * kBsAtomBytes;
+    s.b = o;    o += b_bytes;
+    // an MMA reads 128 rows of its weight slab however many the tile holds: keep 16 KB readable behind the last one
+    if (b_bytes < kBsMmaRows * 128) o += kBsMmaRows * 128 - b_bytes;
+    s.sf = o;   o += fused_kslabs ? (int)align_up((int64_t)fused_kslabs * kBsFusedAtomBytes, 1024) : nsl * kBsAtomBytes;
     s.sfa = o;  o += kBsAtomBytes;
     s.sw = o;   o += (int)align_up((int64_t)nslot_max * skb * 4, 16);
     s.cand = o; o += 4 * mp * 8;                         // lm_head: per epilogue warp and token (value, index)
-    s.bars = o; o += (2 * kMaxStages + 2 * kBsMaxAcc) * 8;
+    s.bars = o; o += (2 * kMaxStages + kBsMaxAcc + 1) * 8;
     s.misc = o; o += 64;
     s.total = o;
     return s;
@@ -154,15 +166,23 @@ __device__ __forceinline__ uint32_t bs_idesc(int n, int sfa, int sfb) {
     return ((uint32_t)sfb << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | (8u << 24) |
            ((uint32_t)sfa << 29);
 }
-// D[tmem] (+)= A[smem] * B[smem] with per-32 scales from tensor memory.
-__device__ __forceinline__ void umma_bs_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t tsfa,
-                                           uint32_t tsfb, uint32_t accumulate) {
+// D[tmem] (+)= A[smem] * B[smem] with per-32 scales from tensor memory.  The descriptors arrive as
+// their 32-bit halves: the upper half is the same for every operand tile, the lower one advances by
+// two (32 bytes) per K block, so the single issuing thread spends two adds per MMA on them.
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma_bs_ss(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t a_hi, uint32_t b_hi,
+                                           uint32_t idesc, uint32_t tsfa, uint32_t tsfb) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %4};\n\t"
+        "setp.ne.b32 p, %8, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, %5, [%6], [%7], p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(a_hi), "r"(b_hi), "r"(idesc), "r"(tsfa), "r"(tsfb), "n"(ACCUMULATE ? 1 : 0)
         : "memory");
 }
+// Halves of the 128B-swizzled K-major operand descriptor (see umma_desc): 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+constexpr uint32_t kUmmaDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
 // One 512-byte scale atom (32 rows x 16 bytes) -> 4 columns of all 128 TMEM lanes.
 __device__ __forceinline__ void tmem_cp_atom(uint32_t taddr, uint64_t sdesc) {
     asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
@@ -203,8 +223,34 @@ __device__ __forceinline__ void tmem_ld_cols<64>(uint32_t taddr, uint32_t (&r)[6
 
 __device__ __forceinline__ void bs_epi_bar() { asm volatile("bar.sync 2, 128;" ::: "memory"); }  // warps 2-5
 
-template <int MP>
+// The sequence of stage items of one CTA.  The shard's rows are cut into tiles of tile_rows rows
+// (at most 128, the M of the MMA; chosen so that the tiles deal out evenly) and CTA c takes tiles
+// [c * T / ncta, (c + 1) * T / ncta) whole, so every output row is a complete dot product inside one
+// CTA and nothing is combined across CTAs.  An item is up to SL consecutive K slabs of one tile.
+struct BsWalk {
+    int t, t1, s, KS, SL;
+    __device__ __forceinline__ BsWalk(int ntiles, int cta, int ncta, int ks, int sl) : s(0), KS(ks), SL(sl) {
+        t = (int)((int64_t)ntiles * cta / ncta);
+        t1 = (int)((int64_t)ntiles * (cta + 1) / ncta);
+    }
+    // next item: tile, first slab, slab count; false when the CTA's tiles are used up
+    __device__ __forceinline__ bool next(int &tile, int &s0, int &nsl) {
+        if (t >= t1) return false;
+        tile = t;
+        s0 = s;
+        nsl = min(SL, KS - s);
+        s += nsl;
+        if (s == KS) {
+            s = 0;
+            ++t;
+        }
+        return true;
+    }
+};
+
+template <int MP, bool FUSED>
 __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_constant__ BsParams p) {
+    static_assert(!FUSED || MP == 16, "the fused form takes at most 8 rows as 16 MMA columns");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     uint8_t *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -214,29 +260,30 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
     const RankCtx &X = A.ctx;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    const int kslabs = p.k >> 7;
+    const int KS = p.k >> 7;                                // slabs per tile
     const int SL = p.slabs_per_stage, NS = p.nstages, NB = p.nacc;
-    const int row_a = (int)((int64_t)cta * p.n / ncta), row_b = (int)((int64_t)(cta + 1) * p.n / ncta);
-    const int items_per_chunk = (kslabs + SL - 1) / SL;
+    const int ntiles = p.ntiles, TR = p.tile_rows;
 
-    const BsSmem S = bs_smem_layout(NS, SL, p.a_pitch, p.b_pitch, p.nslot_max, p.skb, MP);
+    const BsSmem S = bs_smem_layout(NS, SL, p.a_pitch, p.b_pitch, p.nslot_max, p.skb, MP, FUSED ? KS : 0);
     float *sw_s = reinterpret_cast<float *>(smem + S.sw);
     uint32_t *misc_s = reinterpret_cast<uint32_t *>(smem + S.misc);
     const uint32_t a0 = smem_u32(smem + S.a), b0 = smem_u32(smem + S.b), sf0 = smem_u32(smem + S.sf);
-    // full[s]: the stage's bytes landed.  done[s]: every MMA that reads the stage completed.
-    // accfull[b] / accempty[b]: accumulator buffer b holds a finished slab / has been read back.
+    // full[s]: the stage's bytes landed.  done[s]: every MMA that reads the stage has completed (ONE
+    // tcgen05.commit per stage: a commit stalls the issuing thread for ~160 ns, so it is not spent per
+    // slab) -- the producer reads it as "stage free", the epilogue as "this stage's accumulators are
+    // ready".  A stage's slabs accumulate into the SL buffers of accumulator group g = item mod NB;
+    // accempty[g]: the group has been read back.
     const uint32_t full0 = smem_u32(smem + S.bars), done0 = full0 + kMaxStages * 8;
-    const uint32_t accfull0 = done0 + kMaxStages * 8, accempty0 = accfull0 + kBsMaxAcc * 8;
+    const uint32_t accempty0 = done0 + kMaxStages * 8;
+    const uint32_t xready = accempty0 + kBsMaxAcc * 8;  // fused form: the activations are quantised and in place
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(full0 + s * 8, 1);
             mbar_init(done0 + s * 8, 1);
         }
-        for (int b = 0; b < kBsMaxAcc; ++b) {
-            mbar_init(accfull0 + b * 8, 1);
-            mbar_init(accempty0 + b * 8, 4);  // one arrival per epilogue warp
-        }
+        for (int b = 0; b < kBsMaxAcc; ++b) mbar_init(accempty0 + b * 8, 4);  // one arrival per epilogue warp
+        mbar_init(xready, 1);
         mbar_fence_init();
     }
     if (warp == 1) {  // tensor memory: allocated and freed by the same warp
@@ -252,10 +299,10 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(misc_s);
-    // tensor-memory columns: NB accumulator buffers of MP columns, then NB x 4 activation-scale columns
-    // (one scale atom per buffer), then the 4 weight-scale columns
-    const uint32_t t_sfb0 = tmem_base + (uint32_t)(NB * MP);
-    const uint32_t t_sfa = t_sfb0 + (uint32_t)(NB * 4);
+    // tensor-memory columns: NB groups x SL accumulator buffers of MP columns, then 4 activation-scale
+    // columns (one scale atom) per buffer, then 4 weight-scale columns for each of the two issuing threads
+    const uint32_t t_sfb0 = tmem_base + (uint32_t)(NB * SL * MP);
+    const uint32_t t_sfa0 = t_sfb0 + (uint32_t)(NB * SL * 4);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
@@ -263,17 +310,13 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
         if (lane == 0) {
             // Weights are static: the first ring's worth streams before the wait on the prep kernel;
             // the activations and their scales follow once it has finished.
-            const int total_items = p.nchunk * items_per_chunk;
-            auto issue_w = [&](int it) {
-                const int c = it / items_per_chunk, s0 = (it - c * items_per_chunk) * SL;
-                const int nsl = min(SL, kslabs - s0), s = it % NS;
-                const int r0 = row_a + c * p.chunk_rows;
+            const uint32_t slab_tx = (uint32_t)(TR * 128 + (FUSED ? 0 : MP * 128 + kBsAtomBytes));
+            auto issue_w = [&](int s, int tile, int s0, int nsl) {
+                mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)nsl * slab_tx);
                 for (int j = 0; j < nsl; ++j)
-                    tma_load_2d(a0 + (s * SL + j) * p.a_pitch, &p.tmap_w[vr], (s0 + j) * 128, r0, full0 + s * 8);
+                    tma_load_2d(a0 + (s * SL + j) * p.a_pitch, &p.tmap_w[vr], (s0 + j) * 128, tile * TR, full0 + s * 8);
             };
-            auto issue_x = [&](int it) {
-                const int c = it / items_per_chunk, s0 = (it - c * items_per_chunk) * SL;
-                const int nsl = min(SL, kslabs - s0), s = it % NS;
+            auto issue_x = [&](int s, int s0, int nsl) {
                 for (int j = 0; j < nsl; ++j) {
                     tma_load_2d(b0 + (s * SL + j) * p.b_pitch, &p.tmap_x[vr], (s0 + j) * 128, 0, full0 + s * 8);
                     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -281,62 +324,68 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
                                    "r"((uint32_t)kBsAtomBytes), "r"(full0 + s * 8) : "memory");
                 }
             };
-            auto expect = [&](int it) {
-                const int c = it / items_per_chunk, s0 = (it - c * items_per_chunk) * SL;
-                const int nsl = min(SL, kslabs - s0);
-                mbar_arrive_expect_tx(full0 + (it % NS) * 8, (uint32_t)(nsl * (p.chunk_rows * 128 + MP * 128 + kBsAtomBytes)));
-            };
-            const int first = min(NS, total_items);
-            for (int it = 0; it < first; ++it) {
-                expect(it);
-                issue_w(it);
+            int tile, s0, nsl;
+            {   // first lap of the ring: weights at once
+                BsWalk w(ntiles, cta, ncta, KS, SL);
+                for (int item = 0; item < NS && w.next(tile, s0, nsl); ++item) issue_w(item, tile, s0, nsl);
             }
-            if (p.l2_prefetch) {  // the rest of this CTA's weights start towards L2 while the predecessor finishes
-                for (int c = 0; c < p.nchunk; ++c) {
-                    const int r0 = row_a + c * p.chunk_rows, r1 = min(row_b, r0 + p.chunk_rows);
-                    for (int r = r0; r < r1; ++r)
-                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;"
-                                     ::"l"(p.w[vr] + (size_t)r * (size_t)p.ldw[vr]), "r"((uint32_t)p.k) : "memory");
+            if (!FUSED) asm volatile("griddepcontrol.wait;" ::: "memory");  // the fused form's stages hold static weights only
+            BsWalk w(ntiles, cta, ncta, KS, SL);
+            RingPos st;
+            for (int item = 0; w.next(tile, s0, nsl); ++item, st.next(NS)) {
+                const int s = st.s;
+                if (item >= NS) {
+                    if (!mbar_wait(done0 + s * 8, st.ph ^ 1u, X.status)) break;
+                    issue_w(s, tile, s0, nsl);
                 }
-            }
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            for (int it = 0; it < first; ++it) issue_x(it);
-            for (int item = first; item < total_items; ++item) {
-                const int s = item % NS;
-                if (!mbar_wait(done0 + s * 8, (((uint32_t)(item / NS)) & 1u) ^ 1u, X.status)) break;
-                expect(item);
-                issue_w(item);
-                issue_x(item);
+                if (!FUSED) issue_x(s, s0, nsl);
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issue (one thread)
+    } else if (warp == 1 || warp == 6) {
+        // ------------------------------------------------------------ MMA issue (one thread of each warp)
+        // Two threads take the stage items in turn.  Issuing an MMA holds its thread for about as long
+        // as the tensor pipe needs for it, and every item costs a few hundred ns of waits and a commit:
+        // with two issuers one thread's bookkeeping runs while the other's MMAs execute.  Items go to
+        // different stages and accumulator groups, so the two never touch the same memory.
         asm volatile("griddepcontrol.wait;" ::: "memory");
         if (lane == 0) {
+            const int mine = warp == 6 ? 1 : 0;
+            const uint32_t t_sfa = t_sfa0 + (uint32_t)(mine * 4);  // own copy: a copy and the MMAs that read it are ordered only within one thread
             tmem_cp_atom(t_sfa, umma_desc(smem_u32(smem + S.sfa), 128, false));
-            int item = 0, slab_no = 0;
-            bool ok = true;
-            for (int c = 0; c < p.nchunk && ok; ++c) {
-                for (int s0 = 0; s0 < kslabs && ok; s0 += SL, ++item) {
-                    const int nsl = min(SL, kslabs - s0), s = item % NS;
-                    if (!mbar_wait(full0 + s * 8, ((uint32_t)(item / NS)) & 1u, X.status)) { ok = false; break; }
-                    tc_fence_after();
-                    for (int j = 0; j < nsl; ++j, ++slab_no) {
-                        const int tb = slab_no % NB;
-                        if (!mbar_wait(accempty0 + tb * 8, (((uint32_t)(slab_no / NB)) & 1u) ^ 1u, X.status)) { ok = false; break; }
-                        tc_fence_after();
-                        const uint32_t t_acc = tmem_base + (uint32_t)(tb * MP);
-                        const uint32_t t_sfb = t_sfb0 + (uint32_t)(tb * 4);
-                        tmem_cp_atom(t_sfb, umma_desc(sf0 + (s * SL + j) * kBsAtomBytes, 128, false));
-                        const uint32_t a_addr = a0 + (s * SL + j) * p.a_pitch, b_addr = b0 + (s * SL + j) * p.b_pitch;
-#pragma unroll
-                        for (int b = 0; b < 4; ++b)
-                            umma_bs_ss(t_acc, umma_desc(a_addr + b * 32, 1024, true), umma_desc(b_addr + b * 32, 1024, true),
-                                       bs_idesc(MP, 0, b), t_sfa, t_sfb, b ? 1u : 0u);
-                        umma_commit(accfull0 + tb * 8);  // this slab's accumulators are complete
-                    }
-                    umma_commit(done0 + s * 8);          // ... and the stage may be refilled
+            // Everything the loop needs per MMA is an add away: descriptor halves per stage slot, the
+            // four instruction descriptors (one per K block of a slab), ring positions kept incrementally.
+            const uint32_t id0 = bs_idesc(MP, 0, 0), id1 = bs_idesc(MP, 0, 1), id2 = bs_idesc(MP, 0, 2), id3 = bs_idesc(MP, 0, 3);
+            const uint32_t a_lo0 = umma_desc_lo(a0), b_lo0 = umma_desc_lo(b0);
+            const uint32_t a_step = (uint32_t)p.a_pitch >> 4, b_step = (uint32_t)(FUSED ? kBsFusedBBytes : p.b_pitch) >> 4;
+            // fused form: 8 token rows per slab; a stride of 0 between 8-row groups makes MMA columns 8-15
+            // (and rows 8-31 of the scale atom) re-read tokens 0-7
+            const uint32_t b_hi = FUSED ? ((1u << 14) | (2u << 29)) : kUmmaDescHiSw128;
+            const uint64_t sf_desc0 = umma_desc(sf0, FUSED ? 0 : 128, false);
+            const uint32_t sf_step = (uint32_t)(FUSED ? kBsFusedAtomBytes : kBsAtomBytes) >> 4;
+            const bool go = FUSED ? mbar_wait(xready, 0u, X.status) : true;
+            BsWalk w(ntiles, cta, ncta, KS, SL);
+            RingPos st, ag;  // stage ring, accumulator-group ring
+            int tile, s0, nsl;
+            for (int item = 0; go && w.next(tile, s0, nsl); ++item, st.next(NS), ag.next(NB)) {
+                if ((item & 1) != mine) continue;
+                const int s = st.s, g = ag.s;
+                if (!mbar_wait(full0 + s * 8, st.ph, X.status) || !mbar_wait(accempty0 + g * 8, ag.ph ^ 1u, X.status)) break;
+                tc_fence_after();
+                // operands of the item's first slab: the stage slot, or (fused form) the slab's place in the whole K
+                const int bslab = FUSED ? s0 : s * SL;
+                uint32_t a_lo = a_lo0 + (uint32_t)(s * SL) * a_step, b_lo = b_lo0 + (uint32_t)bslab * b_step;
+                uint64_t sf_desc = sf_desc0 + (uint64_t)((uint32_t)bslab * sf_step);
+                uint32_t t_acc = tmem_base + (uint32_t)(g * SL * MP), t_sfb = t_sfb0 + (uint32_t)(g * SL * 4);
+                for (int j = 0; j < nsl; ++j) {
+                    tmem_cp_atom(t_sfb, sf_desc);
+                    umma_bs_ss<false>(t_acc, a_lo, b_lo, kUmmaDescHiSw128, b_hi, id0, t_sfa, t_sfb);
+                    umma_bs_ss<true>(t_acc, a_lo + 2, b_lo + 2, kUmmaDescHiSw128, b_hi, id1, t_sfa, t_sfb);
+                    umma_bs_ss<true>(t_acc, a_lo + 4, b_lo + 4, kUmmaDescHiSw128, b_hi, id2, t_sfa, t_sfb);
+                    umma_bs_ss<true>(t_acc, a_lo + 6, b_lo + 6, kUmmaDescHiSw128, b_hi, id3, t_sfa, t_sfb);
+                    a_lo += a_step; b_lo += b_step; sf_desc += sf_step;
+                    t_acc += MP; t_sfb += 4;
                 }
+                umma_commit(done0 + s * 8);  // the stage may be refilled and its accumulators read
             }
         }
         __syncwarp();
@@ -347,18 +396,58 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
         const uint32_t bank = seq & 1u;
         const int et = tid - 64;                     // 0..127
         const int quad = warp & 3;                   // TMEM lanes this warp may read
-        const int rc = quad * 32 + lane;             // row inside the chunk = TMEM lane
+        const int rc = quad * 32 + lane;             // row inside the tile = TMEM lane
         const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
-        // weight scales of this CTA's rows as fp32: sw_s[slot][column]
+        const int t_lo = (int)((int64_t)ntiles * cta / ncta), t_hi = (int)((int64_t)ntiles * (cta + 1) / ncta) - 1;  // this CTA's tiles
+        // weight scales of the rows this CTA touches as fp32: sw_s[slot][column]
         const int64_t kcol0 = A.k0 >> p.bk_shift;
-        const int64_t srow_lo = (A.row0 + row_a) >> p.bn_shift;
-        const int nslot = row_b > row_a ? (int)(((A.row0 + row_b - 1) >> p.bn_shift) - srow_lo + 1) : 0;
+        const int row_lo = t_lo * TR, row_hi = min(p.n, (t_hi + 1) * TR);
+        const int64_t srow_lo = (A.row0 + row_lo) >> p.bn_shift;
+        const int nslot = row_hi > row_lo ? (int)(((A.row0 + row_hi - 1) >> p.bn_shift) - srow_lo + 1) : 0;
         const int ncols = (int)(((A.k0 + p.k - 1) >> p.bk_shift) - kcol0 + 1);
         for (int i = et; i < nslot * ncols; i += 128) {
             const int sl = i / ncols, c = i - sl * ncols;
             sw_s[sl * p.skb + c] = __ldg(static_cast<const float *>(A.scales) + (srow_lo + sl) * A.scale_ld + kcol0 + c);
         }
+        if constexpr (FUSED) {
+            // The reference's activation quantisation (crates/weightstream-ref/src/actquant.rs:21-57), once per
+            // CTA, straight into the MMA's operand layouts: slab s, token t, 16-byte chunk c at
+            // s * 1024 + t * 128 + ((c ^ t) << 4); exponent of (token t, K block 4 s + j) at s * 128 + t * 16 + j.
+            // Rows of tokens the launch does not carry stay as they are: their MMA columns are never read.
+            uint8_t *bq = smem + S.b, *sfq = smem + S.sf;
+            const int chunks_per_row = p.k >> 3, total = p.m * chunks_per_row;
+            for (int c0 = et; c0 < ((total + 31) & ~31); c0 += 4 * 128) {  // four loads in flight per thread
+                float v[4][8];
+                int tok[4], ch[4];
+                bool valid[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int c = c0 + u * 128;
+                    tok[u] = c / chunks_per_row;
+                    ch[u] = c - tok[u] * chunks_per_row;
+                    valid[u] = c < total;
+                    load_act8(A.x, p.x_dtype, (int64_t)tok[u] * A.ldx + ch[u] * 8, valid[u], v[u]);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (c0 + u * 128 >= ((total + 31) & ~31)) break;  // warp-uniform
+                    int e;
+                    uint32_t lo, hi;
+                    act_quant8(v[u], e, lo, hi);
+                    if (valid[u]) {
+                        const int slab = ch[u] >> 4, c16 = (ch[u] & 15) >> 1, half = ch[u] & 1;
+                        *reinterpret_cast<uint2 *>(bq + slab * kBsFusedBBytes + tok[u] * 128 + ((c16 ^ tok[u]) << 4) + half * 8) = make_uint2(lo, hi);
+                        if ((ch[u] & 3) == 0) {
+                            const int kb = ch[u] >> 2;
+                            sfq[(kb >> 2) * kBsFusedAtomBytes + tok[u] * 16 + (kb & 3)] = (uint8_t)min(max(e + 127, 0), 255);
+                        }
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA and the copy
+        }
         bs_epi_bar();
+        if (FUSED && et == 0) mbar_arrive(xready);
         const int kofs = (int)(A.k0 - kcol0 * ((int64_t)1 << p.bk_shift));
         const bool solo = p.mode == kModeAllReduce && p.world == 1;
         const size_t astride = (size_t)p.lay.max_m * p.lay.max_n;
@@ -367,62 +456,40 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
         uint32_t *ci_s = reinterpret_cast<uint32_t *>(smem + S.cand) + 4 * MP;
         if (p.mode == kModeLmHead)
             for (int i = lane; i < MP; i += 32) { cv_s[(warp - 2) * MP + i] = -INFINITY; ci_s[(warp - 2) * MP + i] = 0xFFFFFFFFu; }
-        int slab_no = 0;
-        bool ok = true;
-        for (int c = 0; c < p.nchunk; ++c) {
-            const int row = row_a + c * p.chunk_rows + rc;
-            const bool mine = rc < p.chunk_rows && row < row_b;
-            // a warp none of whose rows are real only keeps the accumulator buffers moving
-            const bool wactive = quad * 32 < p.chunk_rows && row_a + c * p.chunk_rows + quad * 32 < row_b;
-            const float *swrow = sw_s + (mine ? (int)(((A.row0 + row) >> p.bn_shift) - srow_lo) : 0) * p.skb;
-            float acc[MP];
-#pragma unroll
-            for (int i = 0; i < MP; ++i) acc[i] = 0.0f;
-            for (int sl = 0; sl < kslabs; ++sl, ++slab_no) {
-                const int tb = slab_no % NB;
-                if (ok && !mbar_wait(accfull0 + tb * 8, ((uint32_t)(slab_no / NB)) & 1u, X.status)) ok = false;
-                tc_fence_after();
-                if (wactive && ok) {
-                    const float sw = swrow[(kofs + sl * 128) >> p.bk_shift];
-                    uint32_t r[MP];
-                    tmem_ld_cols<MP>(tlane + (uint32_t)(tb * MP), r);  // returns once the values are in registers
-#pragma unroll
-                    for (int i = 0; i < MP; ++i) acc[i] = fmaf(__uint_as_float(r[i]), sw, acc[i]);
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(accempty0 + tb * 8);
-            }
-            // ---- this chunk's rows are final
+
+        // A finished tile: its rows go to the output, to the peers, or to the gather and the candidates.
+        auto finalize = [&](const float (&v)[MP], int tile) {
+            const int row = tile * TR + rc;
+            const bool mine = rc < TR && row < p.n;
             if (mine) {
                 if (solo) {
 #pragma unroll
                     for (int t = 0; t < MP; ++t)
-                        if (t < p.m) A.out[(size_t)t * p.n + row] = acc[t];
+                        if (t < p.m) A.out[(size_t)t * p.n + row] = v[t];
                 } else if (p.mode == kModeAllReduce) {
                     for (int pr = 0; pr < p.world; ++pr) {
                         uint64_t *dst = reinterpret_cast<uint64_t *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
 #pragma unroll
                         for (int t = 0; t < MP; ++t)
-                            if (t < p.m) st_word_sys(dst + (size_t)t * p.n + row, seq, acc[t]);
+                            if (t < p.m) st_word_sys(dst + (size_t)t * p.n + row, seq, v[t]);
                     }
                 } else if (p.gather_logits) {
                     for (int pr = 0; pr < p.world; ++pr) {
                         float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.gather_off) + (size_t)bank * p.lay.max_m * (size_t)p.lay.max_vocab;
 #pragma unroll
                         for (int t = 0; t < MP; ++t)
-                            if (t < p.m) dst[(size_t)t * p.lay.max_vocab + A.vocab_row0 + row] = acc[t];
+                            if (t < p.m) dst[(size_t)t * p.lay.max_vocab + A.vocab_row0 + row] = v[t];
                     }
                 }
             }
-            if (p.mode == kModeLmHead && wactive) {
+            if (p.mode == kModeLmHead) {
                 // best (value, lowest index) of this warp's rows per token, merged into the warp's running best
                 const uint32_t idx = (uint32_t)(A.vocab_row0 + row);
 #pragma unroll
                 for (int t = 0; t < MP; ++t) {
                     if (t >= p.m) break;
-                    float bv = (mine && acc[t] > -INFINITY) ? acc[t] : -INFINITY;
-                    uint32_t bi = (mine && acc[t] > -INFINITY) ? idx : 0xFFFFFFFFu;
+                    float bv = (mine && v[t] > -INFINITY) ? v[t] : -INFINITY;
+                    uint32_t bi = (mine && v[t] > -INFINITY) ? idx : 0xFFFFFFFFu;
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) {
                         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -435,23 +502,123 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
                     }
                 }
             }
+        };
+
+        BsWalk w(ntiles, cta, ncta, KS, SL);
+        RingPos st, ag;  // stage ring, accumulator-group ring
+        bool ok = true;
+        int tile, s0, nsl;
+        float acc[MP];
+        const float *swrow = sw_s;
+        while (w.next(tile, s0, nsl)) {
+            if (s0 == 0) {  // a new tile
+#pragma unroll
+                for (int i = 0; i < MP; ++i) acc[i] = 0.0f;
+                const int row = min(tile * TR + min(rc, TR - 1), p.n - 1);
+                swrow = sw_s + (int)(((A.row0 + row) >> p.bn_shift) - srow_lo) * p.skb;
+            }
+            const int g = ag.s;
+            if (ok && !mbar_wait(done0 + st.s * 8, st.ph, X.status)) ok = false;
+            ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
+            tc_fence_after();
+            if (ok) {
+                for (int j = 0; j < nsl; ++j) {
+                    const float sw = swrow[(kofs + (s0 + j) * 128) >> p.bk_shift];
+                    uint32_t r[MP];
+                    tmem_ld_cols<MP>(tlane + (uint32_t)((g * SL + j) * MP), r);  // returns once the values are in registers
+#pragma unroll
+                    for (int i = 0; i < MP; ++i) acc[i] = fmaf(__uint_as_float(r[i]), sw, acc[i]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(accempty0 + g * 8);
+            st.next(NS);
+            ag.next(NB);
+            if (s0 + nsl == KS) finalize(acc, tile);  // the tile's rows are final
         }
 
         // ---- exchange (the 128 epilogue threads)
         const uint32_t *myflags = solo ? nullptr
                                        : reinterpret_cast<const uint32_t *>(X.sym[X.rank] + p.lay.flags_off) + (size_t)bank * p.world * nflag;
         if (!solo && p.mode == kModeAllReduce) {
-            // fold the same rows in rank order as the ranks' words arrive
+            // fold the rows of the tiles this CTA finished, in rank order, as the ranks' words arrive
             const uint64_t *slots = reinterpret_cast<const uint64_t *>(X.sym[X.rank] + p.lay.slota_off) + (size_t)bank * p.world * astride;
-            for (int c = 0; c < p.nchunk; ++c) {
-                const int row = row_a + c * p.chunk_rows + rc;
-                if (rc < p.chunk_rows && row < row_b)
-                    for (int t = 0; t < p.m; ++t) {
-                        const size_t off = (size_t)t * p.n + row;
-                        float s = wait_word(slots + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-                        for (int rr = 1; rr < p.world; ++rr)
-                            s += wait_word(slots + rr * astride + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-                        A.out[off] = s;
+            for (int t = t_lo; t <= t_hi; ++t) {
+                const int row = t * TR + rc;
+                if (rc >= TR || row >= p.n) continue;
+                for (int tok = 0; tok < p.m; ++tok) {
+                    const size_t off = (size_t)tok * p.n + row;
+                    float s = wait_word(slots + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
+                    for (int rr = 1; rr < p.world; ++rr)
+                        s += wait_word(slots + rr * astride + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
+                    A.out[off] = s;
+                }
+            }
+        } else if (p.mode == kModeLmHead && !p.gather_logits) {
+            // Only the argmax is wanted.  The CTAs of a rank leave their candidates in the rank's own
+            // table; the CTA that arrives last merges them into ONE (value, lowest index) per token,
+            // sends it to every peer and merges the ranks' candidates: one 64-bit store and one flag
+            // per peer and step instead of one per CTA.
+            bs_epi_bar();
+            uint64_t *table = reinterpret_cast<uint64_t *>(X.sym[X.rank] + p.lay.pairs_off) + (size_t)bank * p.world * kMaxCtas * p.lay.max_m;
+            if (et < p.m) {
+                float bv = cv_s[et];
+                uint32_t bi = ci_s[et];
+                for (int w = 1; w < 4; ++w)
+                    if (cand_better(cv_s[w * MP + et], ci_s[w * MP + et], bv, bi)) { bv = cv_s[w * MP + et]; bi = ci_s[w * MP + et]; }
+                table[((size_t)X.rank * kMaxCtas + cta) * p.lay.max_m + et] = ((uint64_t)__float_as_uint(bv) << 32) | bi;
+            }
+            volatile uint32_t *last_s = misc_s + 4;
+            bs_epi_bar();
+            if (et == 0) {
+                __threadfence();
+                const bool last = atomicAdd(X.counters, 1u) + 1u == (uint32_t)ncta;
+                if (last) {
+                    X.counters[0] = 0u;  // ready for the next step
+                    __threadfence();
+                }
+                *last_s = last ? 1u : 0u;
+            }
+            bs_epi_bar();
+            if (*last_s) {
+                constexpr int kRankRow = kMaxCtas - 1;  // table row of a rank's merged candidate (a rank runs fewer CTAs than that)
+                auto merge = [&](int t, int count, auto entry) {  // warp-wide: best of `count` table entries of token t
+                    float bv = -INFINITY;
+                    uint32_t bi = 0xFFFFFFFFu;
+                    for (int i = lane; i < count; i += 32) {
+                        const uint64_t pr = ld_volatile_u64(entry(i) + t);
+                        const float v = __uint_as_float((uint32_t)(pr >> 32));
+                        const uint32_t idx = (uint32_t)pr;
+                        if (cand_better(v, idx, bv, bi)) { bv = v; bi = idx; }
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                        const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                        if (cand_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+                    }
+                    return ((uint64_t)__float_as_uint(bv) << 32) | bi;
+                };
+                for (int t = warp - 2; t < p.m; t += 4) {
+                    const uint64_t best = merge(t, ncta, [&](int i) { return table + ((size_t)X.rank * kMaxCtas + i) * p.lay.max_m; });
+                    if (lane < p.world) {
+                        uint64_t *dst = reinterpret_cast<uint64_t *>(X.sym[lane] + p.lay.pairs_off) +
+                                        (((size_t)bank * p.world + X.rank) * kMaxCtas + kRankRow) * p.lay.max_m + t;
+                        *dst = best;
+                    }
+                }
+                bs_epi_bar();  // the st.release.sys below is cumulative over the stores this barrier ordered
+                if (et < p.world) {
+                    uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[et] + p.lay.flags_off) + ((size_t)bank * p.world + X.rank) * nflag;
+                    st_release_sys(f + kMaxCtas + 1, seq);
+                    wait_flag(myflags + (size_t)et * nflag + kMaxCtas + 1, seq, p.timeout_ns, X.status, kStatTimeoutGather);
+                }
+                bs_epi_bar();
+                if (A.argmax != nullptr)
+                    for (int t = warp - 2; t < p.m; t += 4) {
+                        const uint64_t best = merge(t, p.world, [&](int i) { return table + ((size_t)i * kMaxCtas + kRankRow) * p.lay.max_m; });
+                        if (lane == 0) A.argmax[t] = ((uint32_t)best == 0xFFFFFFFFu) ? 0u : (uint32_t)best;
                     }
             }
         } else if (p.mode == kModeLmHead) {
