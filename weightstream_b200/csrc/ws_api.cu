@@ -168,13 +168,21 @@ ws_status_t set_smem(ws_tp *tp, K kernel) {
 
 template <typename P>
 ws_status_t launch(ws_tp *tp, void (*kernel)(P), const P &params, int ncta, int nvr, int threads, size_t smem,
-                   cudaStream_t stream, bool pdl = false, bool waits_on_peers = true) {
+                   cudaStream_t stream, bool pdl = false, bool waits_on_peers = true, int cluster = 1) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)ncta, (unsigned)nvr, 1);
     cfg.blockDim = dim3((unsigned)threads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
+    cfg.numAttrs = 1;
+    if (cluster > 1) {  // CTA pairs sharing distributed shared memory (never together with virtual ranks)
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = (unsigned)cluster;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
     if (nvr > 1 && waits_on_peers) {
         // Virtual ranks sharing one device wait on one another inside the kernel: they must be
         // co-resident, which a cooperative launch guarantees (or refuses).
@@ -188,7 +196,6 @@ ws_status_t launch(ws_tp *tp, void (*kernel)(P), const P &params, int ncta, int 
         attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
     }
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
     WS_CUDA(tp, cudaLaunchKernelEx(&cfg, kernel, params));
     tp->launches++;
     return WS_OK;
@@ -265,8 +272,8 @@ ws_status_t ws_tp_create(int32_t world, int32_t rank, int32_t device, const ws_t
     if (world == 1) tp->connected = true;
     if (set_smem(tp, moe_gemv_kernel) != WS_OK || set_smem(tp, fp8_rowpar_kernel<0>) != WS_OK || set_smem(tp, fp8_rowpar_kernel<1>) != WS_OK ||
         set_smem(tp, fp8_rowpar_kernel<2>) != WS_OK || set_smem(tp, moe_down_kernel) != WS_OK ||
-        set_smem(tp, fp8_bs_kernel<16, true>) != WS_OK || set_smem(tp, fp8_bs_kernel<16, false>) != WS_OK ||
-        set_smem(tp, fp8_bs_kernel<32, false>) != WS_OK || set_smem(tp, fp8_bs_kernel<64, false>) != WS_OK)
+        set_smem(tp, fp8_bs_kernel<16>) != WS_OK || set_smem(tp, fp8_bs_kernel<32>) != WS_OK ||
+        set_smem(tp, fp8_bs_kernel<64>) != WS_OK)
         return bail(WS_ERR_CUDA);
     *out = tp;
     return WS_OK;
@@ -402,41 +409,47 @@ static ws_status_t validate_fp8(ws_tp *tp, const ws_fp8_gemm_args_t &a, bool lm_
 struct BsPlan {
     bool ok;
     int mp, tile_rows, ntiles, a_pitch, b_pitch, slabs_per_stage, nstages, nslot_max, nacc;
-    int fused;  // 1: at most 8 rows, quantised inside the kernel and kept in shared memory for the whole K (no prep kernel)
+    int csize;  // 2: CTA pairs share a tile, each CTA streams half of K (tiles of a lone CTA would fill under half of the MMA's rows)
+    int ncta;   // CTAs the plan is for (even with pairs)
     size_t smem;
 };
-static BsPlan bs_plan(const ws_fp8_gemm_args_t &a, int mt, int skb, int ncta) {
+static BsPlan bs_plan(const ws_fp8_gemm_args_t &a, int mt, int skb, int ncta, bool pairs_allowed) {
     BsPlan u{};
     if (a.scale_kind != WS_SCALE_F32 || a.block_k % 128 || a.k % 128 || mt > kBsMaxTokens) return u;
     u.mp = mt <= 16 ? 16 : mt <= 32 ? 32 : 64;
     // tiles of equal height that deal out evenly: a CTA's share of the rows, cut into as few pieces
     // of at most 128 rows as possible
-    const int crmax = (a.n + ncta - 1) / ncta;
+    const int kslabs = a.k / 128;
+    // The tensor pipe spends the same time on an MMA however few of its 128 rows are real.  When a
+    // CTA's share of the rows fills under half of them, two CTAs share a tile and split K instead.
+    u.csize = (pairs_allowed && ncta >= 2 && kslabs >= 2 && (a.n + ncta - 1) / ncta <= kBsMmaRows / 2) ? 2 : 1;
+    u.ncta = u.csize == 2 ? ncta & ~1 : ncta;
+    const int nparts = u.ncta / u.csize;
+    const int crmax = (a.n + nparts - 1) / nparts;
     const int pieces = (crmax + kBsMmaRows - 1) / kBsMmaRows;
     u.tile_rows = (crmax + pieces - 1) / pieces;
     u.ntiles = (a.n + u.tile_rows - 1) / u.tile_rows;
-    const int tiles_per_cta = (u.ntiles + ncta - 1) / ncta;
+    const int tiles_per_cta = (u.ntiles + nparts - 1) / nparts;
     u.a_pitch = (u.tile_rows + 7) / 8 * 8 * 128;
     u.b_pitch = u.mp * 128;
-    const int kslabs = a.k / 128;
-    u.fused = mt <= kBsFusedTokens ? 1 : 0;
-    const int slab_bytes = u.fused ? u.a_pitch : u.a_pitch + u.b_pitch + kBsAtomBytes;
+    const int slab_bytes = u.a_pitch + u.b_pitch + kBsAtomBytes;
     // slabs per stage: one MMA commit (a ~160 ns stall of the issuing thread) per stage, so several
     // slabs share it; bounded by the stage size and by tensor memory (each slab has its own
     // accumulator buffer: groups x slabs x (mp + 4) + 8 columns of 512, at least two groups)
     u.slabs_per_stage = std::max(1, std::min({4, (56 * 1024) / slab_bytes, 504 / (2 * (u.mp + 4)), kslabs}));
     u.nslot_max = (tiles_per_cta * u.tile_rows) / a.block_n + 2;
     u.nacc = std::min((int)kBsMaxAcc, 504 / (u.slabs_per_stage * (u.mp + 4)));
-    const int fixed = bs_smem_layout(0, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp, u.fused ? kslabs : 0).total;
+    const int rx_rows = u.csize == 2 ? mt : 0;
+    const int fixed = bs_smem_layout(0, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp, rx_rows).total;
     int ns = (kSmemBudget - fixed - 1024 - kBsMmaRows * 128) / (u.slabs_per_stage * slab_bytes);
-    const int items = tiles_per_cta * ((kslabs + u.slabs_per_stage - 1) / u.slabs_per_stage);
+    const int items = tiles_per_cta * ((kslabs / u.csize + u.slabs_per_stage - 1) / u.slabs_per_stage);
     ns = std::min(ns, std::min((int)kMaxStages, std::max(2, items)));
     u.nstages = ns;
     // the epilogue and the producer wait on the same per-stage barrier: the MMA thread must not get a
     // whole lap of the stage ring ahead of the epilogue, which holds when groups <= stages
     u.nacc = std::max(1, std::min(u.nacc, ns));
     u.ok = ns >= 2;
-    if (u.ok) u.smem = (size_t)bs_smem_layout(ns, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp, u.fused ? kslabs : 0).total + 1024;
+    if (u.ok) u.smem = (size_t)bs_smem_layout(ns, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp, rx_rows).total + 1024;
     return u;
 }
 
@@ -468,7 +481,8 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
     p.vocab = lm ? lm[0].vocab : 0;
     p.tile_rows = u.tile_rows; p.ntiles = u.ntiles; p.a_pitch = u.a_pitch; p.b_pitch = u.b_pitch;
     p.slabs_per_stage = u.slabs_per_stage; p.nstages = u.nstages; p.nslot_max = u.nslot_max; p.skb = skb; p.nacc = u.nacc;
-    p.x_dtype = a0.x_dtype;
+    p.csize = u.csize;
+    ncta = u.ncta;
     p.timeout_ns = t0->timeout_ns;
     p.lay = t0->lay;
     ActPrepParams q{};
@@ -480,14 +494,14 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
         ws_tp *t = ranks[i];
         const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
         if (lm && lm[i].logits) p.gather_logits = 1;
-        ws_status_t s = u.fused ? WS_OK : ensure_bs_scratch(t, xq_bytes + sf_bytes);
+        ws_status_t s = ensure_bs_scratch(t, xq_bytes + sf_bytes);
         if (s == WS_OK) s = make_tmap(t, &p.tmap_w[i], a.w, (uint64_t)a.n, (uint64_t)a.k, (uint64_t)a.ldw, (uint32_t)u.tile_rows);
         uint8_t *const xq = t->bs_work;
-        if (s == WS_OK && !u.fused) s = make_tmap(t, &p.tmap_x[i], xq, (uint64_t)u.mp, (uint64_t)a.k, (uint64_t)a.k, (uint32_t)u.mp);
+        if (s == WS_OK) s = make_tmap(t, &p.tmap_x[i], xq, (uint64_t)u.mp, (uint64_t)a.k, (uint64_t)a.k, (uint32_t)u.mp);
         if (s != WS_OK) { t0->err = t->err; return s; }
         Fp8RankArgs &r = p.r[i];
         const size_t xes = a.x_dtype == WS_ACT_BF16 ? 2 : 4;
-        r.x = static_cast<const char *>(a.x) + (size_t)m0 * a.ldx * xes;  // read by the fused form only
+        r.x = nullptr;
         r.scales = a.scales;
         r.out = lm ? nullptr : a.out + (size_t)m0 * a.n;
         r.logits = lm && lm[i].logits ? lm[i].logits + (size_t)m0 * lm[i].vocab : nullptr;
@@ -502,17 +516,14 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
         q.r[i].ldx = a.ldx;
     }
     for (int i = 0; i < n; ++i) ranks[i]->step++;
-    void (*const kernel)(BsParams) = u.fused ? fp8_bs_kernel<16, true>
-                                     : u.mp == 16 ? fp8_bs_kernel<16, false>
-                                     : u.mp == 32 ? fp8_bs_kernel<32, false>
-                                                  : fp8_bs_kernel<64, false>;
+    void (*const kernel)(BsParams) = u.mp == 16 ? fp8_bs_kernel<16> : u.mp == 32 ? fp8_bs_kernel<32> : fp8_bs_kernel<64>;
     const int prep_blocks = (int)(((int64_t)u.mp * (a0.k / 8) + 255) / 256);
     if (same_device) {
         WS_CUDA(t0, cudaSetDevice(t0->device));
         cudaStream_t cs = static_cast<cudaStream_t>(streams ? streams[0] : nullptr);
-        ws_status_t s = u.fused ? WS_OK : launch(t0, act_prep_kernel, q, prep_blocks, n, 256, 0, cs, t0->pdl != 0, false);
+        ws_status_t s = launch(t0, act_prep_kernel, q, prep_blocks, n, 256, 0, cs, t0->pdl != 0, false);
         if (s != WS_OK) return s;
-        return launch(t0, kernel, p, ncta, n, kBsThreads, u.smem, cs, t0->pdl != 0);
+        return launch(t0, kernel, p, ncta, n, kBsThreads, u.smem, cs, t0->pdl != 0, true, u.csize);
     }
     for (int i = 0; i < n; ++i) {
         BsParams pi = p;
@@ -524,17 +535,21 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
         qi.r[0] = q.r[i];
         WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
         cudaStream_t cs = static_cast<cudaStream_t>(streams ? streams[i] : nullptr);
-        ws_status_t s = u.fused ? WS_OK : launch(ranks[i], act_prep_kernel, qi, prep_blocks, 1, 256, 0, cs, t0->pdl != 0, false);
-        if (s == WS_OK) s = launch(ranks[i], kernel, pi, ncta, 1, kBsThreads, u.smem, cs, t0->pdl != 0);
+        ws_status_t s = launch(ranks[i], act_prep_kernel, qi, prep_blocks, 1, 256, 0, cs, t0->pdl != 0, false);
+        if (s == WS_OK) s = launch(ranks[i], kernel, pi, ncta, 1, kBsThreads, u.smem, cs, t0->pdl != 0, true, u.csize);
         if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
     }
     return WS_OK;
 }
 
 // Whether rows [.., +mt) of this step go to the block-scaled tcgen05 path: always when the caller
-// selected it, by default from three rows up (one and two rows run on CUDA cores).
-static bool bs_wanted(const ws_tp *t0, int mt) {
-    return t0->kernel_sel == 2 || (t0->kernel_sel == 0 && mt >= 3);
+// selected it; by default from three rows up, and for one or two rows when the shard is large enough
+// for its streaming rate to outweigh the second launch (measured on B200, M=1: 58.7 MB 16.4 us against
+// 17.2 us on CUDA cores, 927 MB 153 against 208 us; 14.7 MB 8.8 against 6.8 us, 7.3 MB 12.8 against 5.9 us).
+static bool bs_wanted(const ws_tp *t0, int mt, const ws_fp8_gemm_args_t &a) {
+    if (t0->kernel_sel == 2) return true;
+    if (t0->kernel_sel != 0) return false;
+    return mt >= 3 || (int64_t)a.n * a.k >= ((int64_t)32 << 20);
 }
 
 // Activation rows the next launch takes: up to 64 when their quantised copies fit in shared
@@ -544,7 +559,7 @@ static int fp8_rows_per_launch(const ws_tp *t0, const ws_fp8_gemm_args_t &a, int
     {   // the tensor-memory path streams the weights once for up to 64 rows
         const int mt = std::min(rem, (int)kBsMaxTokens);
         const int skb = (int)((a.k0 + a.k - 1) / a.block_k - a.k0 / a.block_k + 1);
-        if (bs_wanted(t0, mt) && bs_plan(a, mt, skb, ncta).ok) return mt;
+        if (bs_wanted(t0, mt, a) && bs_plan(a, mt, skb, ncta, false).ok) return mt;
     }
     if (rem <= 8) return rem;
     const int kbox = (a.k + 127) / 128;
@@ -563,13 +578,13 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
                             int m0, int mt, void *const *streams, int ncta, bool same_device) {
     ws_tp *t0 = ranks[0];
     const ws_fp8_gemm_args_t &a0 = lm ? lm[0].g : args[0];
-    if (bs_wanted(t0, mt)) {  // tensor-memory path whenever the shape fits it
+    if (bs_wanted(t0, mt, a0)) {  // tensor-memory path whenever the shape fits it
         int64_t skb_u = 1;
         for (int i = 0; i < n; ++i) {
             const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
             skb_u = std::max<int64_t>(skb_u, (a.k0 + a.k - 1) / a.block_k - a.k0 / a.block_k + 1);
         }
-        const BsPlan u = bs_plan(a0, mt, (int)skb_u, ncta);
+        const BsPlan u = bs_plan(a0, mt, (int)skb_u, ncta, n == 1);  // CTA pairs need a cluster launch, virtual ranks a cooperative one
         if (u.ok) return bs_step(ranks, n, args, lm, m0, mt, streams, ncta, same_device, u, (int)skb_u);
     }
     Fp8Params p{};

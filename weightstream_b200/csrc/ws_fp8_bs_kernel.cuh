@@ -47,9 +47,6 @@ constexpr int kBsMaxAcc = 8;         // accumulator groups in tensor memory (a g
 constexpr int kBsMaxTokens = 64;     // activation rows one launch takes
 constexpr int kBsAtomBytes = 512;    // one scale atom: 128 rows x 4 K blocks
 constexpr int kBsMmaRows = 128;      // M of the MMA; a tile of output rows holds at most as many
-constexpr int kBsFusedTokens = 8;    // most activation rows the fused form (no prep kernel) takes
-constexpr int kBsFusedBBytes = 1024; // fused form, per K slab: 8 token rows x 128 bytes (MMA columns 8-15 re-read them)
-constexpr int kBsFusedAtomBytes = 128;  // fused form, per K slab: the 8 tokens' rows of the scale atom
 
 // ---------------------------------------------------------------- activation prep
 struct ActPrepRank {
@@ -97,38 +94,37 @@ struct alignas(64) BsParams {
     CUtensorMap tmap_x[WS_MAX_WORLD];  // quantised activations [mp][k bytes], box 128 bytes x mp, 128B swizzle
     int32_t m, mp, n, k, bn_shift, bk_shift;
     int32_t world, mode, vocab, gather_logits;
-    int32_t x_dtype, pad0;             // fused form only: element type of r[].x
+    int32_t pad0;
+    int32_t csize;                     // 1, or 2: CTA pairs (a cluster) share a tile, each streams half of K
     int32_t tile_rows, ntiles;         // output rows per tile (<= 128) and tiles of the shard
     int32_t slabs_per_stage, nstages;
     int32_t a_pitch, b_pitch;          // bytes one slab's weights / activations occupy in a stage (multiples of 1024)
     int32_t skb, nslot_max, nacc;
     uint64_t timeout_ns;
     SymLayout lay;
-    Fp8RankArgs r[WS_MAX_WORLD];       // x: fused form only; scales/out/logits/argmax/row0/k0/ctx as in the decode kernel
+    Fp8RankArgs r[WS_MAX_WORLD];       // x is unused here; scales/out/logits/argmax/row0/k0/ctx as in the decode kernel
     const uint8_t *sfb[WS_MAX_WORLD];  // the prep kernel's scale atoms
 };
 
 struct BsSmem {
-    int32_t a, b, sf, sfa, sw, cand, bars, misc, total;
+    int32_t a, b, sf, sfa, sw, cand, rx, bars, misc, total;
 };
-// fused_kslabs = 0: activations and their scale atoms travel through the stages (prep-kernel form).
-// fused_kslabs = k / 128: the kernel quantises its (at most 8) activation rows itself and keeps them
-// for the whole K: 8 rows x 128 bytes and a 128-byte scale atom per slab; the stages hold weights only.
 __host__ __device__ inline BsSmem bs_smem_layout(int nstages, int slabs_per_stage, int a_pitch, int b_pitch, int nslot_max,
-                                                 int skb, int mp, int fused_kslabs) {
+                                                 int skb, int mp, int rx_rows) {
     BsSmem s{};
     const int nsl = nstages * slabs_per_stage;
-    const int b_bytes = fused_kslabs ? fused_kslabs * kBsFusedBBytes : nsl * b_pitch;
+    const int b_bytes = nsl * b_pitch;
     int o = 0;
     s.a = o;    o += nsl * a_pitch;
     s.b = o;    o += b_bytes;
     // an MMA reads 128 rows of its weight slab however many the tile holds: keep 16 KB readable behind the last one
     if (b_bytes < kBsMmaRows * 128) o += kBsMmaRows * 128 - b_bytes;
-    s.sf = o;   o += fused_kslabs ? (int)align_up((int64_t)fused_kslabs * kBsFusedAtomBytes, 1024) : nsl * kBsAtomBytes;
+    s.sf = o;   o += nsl * kBsAtomBytes;
     s.sfa = o;  o += kBsAtomBytes;
     s.sw = o;   o += (int)align_up((int64_t)nslot_max * skb * 4, 16);
     s.cand = o; o += 4 * mp * 8;                         // lm_head: per epilogue warp and token (value, index)
-    s.bars = o; o += (2 * kMaxStages + kBsMaxAcc + 1) * 8;
+    s.rx = o;   o += rx_rows * kBsMmaRows * 4;           // CTA pairs: the partner's partial sums of one tile, [token][row]
+    s.bars = o; o += (2 * kMaxStages + kBsMaxAcc + 2) * 8;
     s.misc = o; o += 64;
     s.total = o;
     return s;
@@ -221,36 +217,72 @@ __device__ __forceinline__ void tmem_ld_cols<64>(uint32_t taddr, uint32_t (&r)[6
 #undef WS_R16
 #undef WS_R4
 
+// ---- distributed shared memory of a CTA pair
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, uint32_t cta_rank) {  // the same address in CTA `cta_rank` of the cluster
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(cta_rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar) {  // releases this thread's earlier stores to the cluster
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+// Wait on an own barrier that the partner CTA arrives on; bounded like mbar_wait.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint32_t *status) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((++spins & 63u) == 0u) {
+            if (*(volatile uint32_t *)status != 0u) return false;
+            if (globaltimer_ns() - t0 > 2000000000ull) break;
+        }
+    }
+    atomicCAS(status, 0u, kStatTimeoutTma | (uint32_t)(-WS_ERR_TIMEOUT));
+    return false;
+}
+
 __device__ __forceinline__ void bs_epi_bar() { asm volatile("bar.sync 2, 128;" ::: "memory"); }  // warps 2-5
 
 // The sequence of stage items of one CTA.  The shard's rows are cut into tiles of tile_rows rows
 // (at most 128, the M of the MMA; chosen so that the tiles deal out evenly) and CTA c takes tiles
 // [c * T / ncta, (c + 1) * T / ncta) whole, so every output row is a complete dot product inside one
 // CTA and nothing is combined across CTAs.  An item is up to SL consecutive K slabs of one tile.
+// With CTA pairs (csize = 2) the tiles are dealt out to the pairs and each CTA of a pair walks one
+// half of every tile's K slabs; the second CTA hands its sums to the first through the pair's
+// distributed shared memory (see the epilogue).
 struct BsWalk {
-    int t, t1, s, KS, SL;
-    __device__ __forceinline__ BsWalk(int ntiles, int cta, int ncta, int ks, int sl) : s(0), KS(ks), SL(sl) {
-        t = (int)((int64_t)ntiles * cta / ncta);
-        t1 = (int)((int64_t)ntiles * (cta + 1) / ncta);
+    int t, t1, s, K0, K1, SL;  // tiles [t, t1), slabs [K0, K1) of each
+    __device__ __forceinline__ BsWalk(int ntiles, int part, int nparts, int k0, int k1, int sl) : s(k0), K0(k0), K1(k1), SL(sl) {
+        t = (int)((int64_t)ntiles * part / nparts);
+        t1 = (int)((int64_t)ntiles * (part + 1) / nparts);
+        if (k1 <= k0) t1 = t;
     }
     // next item: tile, first slab, slab count; false when the CTA's tiles are used up
     __device__ __forceinline__ bool next(int &tile, int &s0, int &nsl) {
         if (t >= t1) return false;
         tile = t;
         s0 = s;
-        nsl = min(SL, KS - s);
+        nsl = min(SL, K1 - s);
         s += nsl;
-        if (s == KS) {
-            s = 0;
+        if (s == K1) {
+            s = K0;
             ++t;
         }
         return true;
     }
 };
 
-template <int MP, bool FUSED>
+template <int MP>
 __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_constant__ BsParams p) {
-    static_assert(!FUSED || MP == 16, "the fused form takes at most 8 rows as 16 MMA columns");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     uint8_t *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -261,10 +293,15 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     const int KS = p.k >> 7;                                // slabs per tile
+    // CTA pairs: which half of K is this CTA's, and which pair of how many it belongs to
+    uint32_t crank = 0;
+    if (p.csize == 2) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+    const int part = p.csize == 2 ? cta >> 1 : cta, nparts = p.csize == 2 ? ncta >> 1 : ncta;
+    const int k_lo = (int)crank * KS / p.csize, k_hi = ((int)crank + 1) * KS / p.csize;
     const int SL = p.slabs_per_stage, NS = p.nstages, NB = p.nacc;
     const int ntiles = p.ntiles, TR = p.tile_rows;
 
-    const BsSmem S = bs_smem_layout(NS, SL, p.a_pitch, p.b_pitch, p.nslot_max, p.skb, MP, FUSED ? KS : 0);
+    const BsSmem S = bs_smem_layout(NS, SL, p.a_pitch, p.b_pitch, p.nslot_max, p.skb, MP, p.csize == 2 ? p.m : 0);
     float *sw_s = reinterpret_cast<float *>(smem + S.sw);
     uint32_t *misc_s = reinterpret_cast<uint32_t *>(smem + S.misc);
     const uint32_t a0 = smem_u32(smem + S.a), b0 = smem_u32(smem + S.b), sf0 = smem_u32(smem + S.sf);
@@ -275,7 +312,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
     // accempty[g]: the group has been read back.
     const uint32_t full0 = smem_u32(smem + S.bars), done0 = full0 + kMaxStages * 8;
     const uint32_t accempty0 = done0 + kMaxStages * 8;
-    const uint32_t xready = accempty0 + kBsMaxAcc * 8;  // fused form: the activations are quantised and in place
+    const uint32_t rxfull = accempty0 + kBsMaxAcc * 8, rxempty = rxfull + 8;  // CTA pairs: the partner's sums of a tile have arrived / been read
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
@@ -283,14 +320,15 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
             mbar_init(done0 + s * 8, 1);
         }
         for (int b = 0; b < kBsMaxAcc; ++b) mbar_init(accempty0 + b * 8, 4);  // one arrival per epilogue warp
-        mbar_init(xready, 1);
+        mbar_init(rxfull, 128);   // every epilogue thread of the partner arrives after its stores
+        mbar_init(rxempty, 128);
         mbar_fence_init();
     }
     if (warp == 1) {  // tensor memory: allocated and freed by the same warp
         tmem_alloc(smem_u32(misc_s), kBsTmemCols);
         tmem_relinquish();
     }
-    if (warp >= 2) {  // the weight operand's scale atom: 2^0 everywhere
+    if (warp >= 2 && warp < 6) {  // the weight operand's scale atom: 2^0 everywhere (128 threads x 4 bytes)
         uint32_t *sfa = reinterpret_cast<uint32_t *>(smem + S.sfa);
         sfa[tid - 64] = 0x7F7F7F7Fu;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -298,6 +336,10 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    if (p.csize == 2) {  // the partner's barriers are initialised before anything is sent to them
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(misc_s);
     // tensor-memory columns: NB groups x SL accumulator buffers of MP columns, then 4 activation-scale
     // columns (one scale atom) per buffer, then 4 weight-scale columns for each of the two issuing threads
@@ -306,11 +348,11 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
-        // ------------------------------------------------------------ producer
+        // ------------------------------------------------------------ producer (one thread)
         if (lane == 0) {
             // Weights are static: the first ring's worth streams before the wait on the prep kernel;
             // the activations and their scales follow once it has finished.
-            const uint32_t slab_tx = (uint32_t)(TR * 128 + (FUSED ? 0 : MP * 128 + kBsAtomBytes));
+            const uint32_t slab_tx = (uint32_t)(TR * 128 + MP * 128 + kBsAtomBytes);
             auto issue_w = [&](int s, int tile, int s0, int nsl) {
                 mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)nsl * slab_tx);
                 for (int j = 0; j < nsl; ++j)
@@ -326,11 +368,11 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
             };
             int tile, s0, nsl;
             {   // first lap of the ring: weights at once
-                BsWalk w(ntiles, cta, ncta, KS, SL);
+                BsWalk w(ntiles, part, nparts, k_lo, k_hi, SL);
                 for (int item = 0; item < NS && w.next(tile, s0, nsl); ++item) issue_w(item, tile, s0, nsl);
             }
-            if (!FUSED) asm volatile("griddepcontrol.wait;" ::: "memory");  // the fused form's stages hold static weights only
-            BsWalk w(ntiles, cta, ncta, KS, SL);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            BsWalk w(ntiles, part, nparts, k_lo, k_hi, SL);
             RingPos st;
             for (int item = 0; w.next(tile, s0, nsl); ++item, st.next(NS)) {
                 const int s = st.s;
@@ -338,7 +380,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
                     if (!mbar_wait(done0 + s * 8, st.ph ^ 1u, X.status)) break;
                     issue_w(s, tile, s0, nsl);
                 }
-                if (!FUSED) issue_x(s, s0, nsl);
+                issue_x(s, s0, nsl);
             }
         }
     } else if (warp == 1 || warp == 6) {
@@ -356,32 +398,26 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
             // four instruction descriptors (one per K block of a slab), ring positions kept incrementally.
             const uint32_t id0 = bs_idesc(MP, 0, 0), id1 = bs_idesc(MP, 0, 1), id2 = bs_idesc(MP, 0, 2), id3 = bs_idesc(MP, 0, 3);
             const uint32_t a_lo0 = umma_desc_lo(a0), b_lo0 = umma_desc_lo(b0);
-            const uint32_t a_step = (uint32_t)p.a_pitch >> 4, b_step = (uint32_t)(FUSED ? kBsFusedBBytes : p.b_pitch) >> 4;
-            // fused form: 8 token rows per slab; a stride of 0 between 8-row groups makes MMA columns 8-15
-            // (and rows 8-31 of the scale atom) re-read tokens 0-7
-            const uint32_t b_hi = FUSED ? ((1u << 14) | (2u << 29)) : kUmmaDescHiSw128;
-            const uint64_t sf_desc0 = umma_desc(sf0, FUSED ? 0 : 128, false);
-            const uint32_t sf_step = (uint32_t)(FUSED ? kBsFusedAtomBytes : kBsAtomBytes) >> 4;
-            const bool go = FUSED ? mbar_wait(xready, 0u, X.status) : true;
-            BsWalk w(ntiles, cta, ncta, KS, SL);
+            const uint32_t a_step = (uint32_t)p.a_pitch >> 4, b_step = (uint32_t)p.b_pitch >> 4;
+            const uint64_t sf_desc0 = umma_desc(sf0, 128, false);
+            const uint32_t sf_step = (uint32_t)kBsAtomBytes >> 4;
+            BsWalk w(ntiles, part, nparts, k_lo, k_hi, SL);
             RingPos st, ag;  // stage ring, accumulator-group ring
             int tile, s0, nsl;
-            for (int item = 0; go && w.next(tile, s0, nsl); ++item, st.next(NS), ag.next(NB)) {
+            for (int item = 0; w.next(tile, s0, nsl); ++item, st.next(NS), ag.next(NB)) {
                 if ((item & 1) != mine) continue;
                 const int s = st.s, g = ag.s;
                 if (!mbar_wait(full0 + s * 8, st.ph, X.status) || !mbar_wait(accempty0 + g * 8, ag.ph ^ 1u, X.status)) break;
                 tc_fence_after();
-                // operands of the item's first slab: the stage slot, or (fused form) the slab's place in the whole K
-                const int bslab = FUSED ? s0 : s * SL;
-                uint32_t a_lo = a_lo0 + (uint32_t)(s * SL) * a_step, b_lo = b_lo0 + (uint32_t)bslab * b_step;
-                uint64_t sf_desc = sf_desc0 + (uint64_t)((uint32_t)bslab * sf_step);
+                uint32_t a_lo = a_lo0 + (uint32_t)(s * SL) * a_step, b_lo = b_lo0 + (uint32_t)(s * SL) * b_step;
+                uint64_t sf_desc = sf_desc0 + (uint64_t)((uint32_t)(s * SL) * sf_step);
                 uint32_t t_acc = tmem_base + (uint32_t)(g * SL * MP), t_sfb = t_sfb0 + (uint32_t)(g * SL * 4);
                 for (int j = 0; j < nsl; ++j) {
                     tmem_cp_atom(t_sfb, sf_desc);
-                    umma_bs_ss<false>(t_acc, a_lo, b_lo, kUmmaDescHiSw128, b_hi, id0, t_sfa, t_sfb);
-                    umma_bs_ss<true>(t_acc, a_lo + 2, b_lo + 2, kUmmaDescHiSw128, b_hi, id1, t_sfa, t_sfb);
-                    umma_bs_ss<true>(t_acc, a_lo + 4, b_lo + 4, kUmmaDescHiSw128, b_hi, id2, t_sfa, t_sfb);
-                    umma_bs_ss<true>(t_acc, a_lo + 6, b_lo + 6, kUmmaDescHiSw128, b_hi, id3, t_sfa, t_sfb);
+                    umma_bs_ss<false>(t_acc, a_lo, b_lo, kUmmaDescHiSw128, kUmmaDescHiSw128, id0, t_sfa, t_sfb);
+                    umma_bs_ss<true>(t_acc, a_lo + 2, b_lo + 2, kUmmaDescHiSw128, kUmmaDescHiSw128, id1, t_sfa, t_sfb);
+                    umma_bs_ss<true>(t_acc, a_lo + 4, b_lo + 4, kUmmaDescHiSw128, kUmmaDescHiSw128, id2, t_sfa, t_sfb);
+                    umma_bs_ss<true>(t_acc, a_lo + 6, b_lo + 6, kUmmaDescHiSw128, kUmmaDescHiSw128, id3, t_sfa, t_sfb);
                     a_lo += a_step; b_lo += b_step; sf_desc += sf_step;
                     t_acc += MP; t_sfb += 4;
                 }
@@ -391,15 +427,13 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
         __syncwarp();
     } else {
         // ------------------------------------------------------------ epilogue warps 2-5
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        const uint32_t seq = step_begin(X);
-        const uint32_t bank = seq & 1u;
         const int et = tid - 64;                     // 0..127
         const int quad = warp & 3;                   // TMEM lanes this warp may read
         const int rc = quad * 32 + lane;             // row inside the tile = TMEM lane
         const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
-        const int t_lo = (int)((int64_t)ntiles * cta / ncta), t_hi = (int)((int64_t)ntiles * (cta + 1) / ncta) - 1;  // this CTA's tiles
-        // weight scales of the rows this CTA touches as fp32: sw_s[slot][column]
+        const int t_lo = (int)((int64_t)ntiles * part / nparts), t_hi = (int)((int64_t)ntiles * (part + 1) / nparts) - 1;  // this CTA's tiles
+        // weight scales of the rows this CTA touches as fp32: sw_s[slot][column].  They are static, so
+        // they are fetched before the wait on the predecessor.
         const int64_t kcol0 = A.k0 >> p.bk_shift;
         const int row_lo = t_lo * TR, row_hi = min(p.n, (t_hi + 1) * TR);
         const int64_t srow_lo = (A.row0 + row_lo) >> p.bn_shift;
@@ -409,45 +443,10 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
             const int sl = i / ncols, c = i - sl * ncols;
             sw_s[sl * p.skb + c] = __ldg(static_cast<const float *>(A.scales) + (srow_lo + sl) * A.scale_ld + kcol0 + c);
         }
-        if constexpr (FUSED) {
-            // The reference's activation quantisation (crates/weightstream-ref/src/actquant.rs:21-57), once per
-            // CTA, straight into the MMA's operand layouts: slab s, token t, 16-byte chunk c at
-            // s * 1024 + t * 128 + ((c ^ t) << 4); exponent of (token t, K block 4 s + j) at s * 128 + t * 16 + j.
-            // Rows of tokens the launch does not carry stay as they are: their MMA columns are never read.
-            uint8_t *bq = smem + S.b, *sfq = smem + S.sf;
-            const int chunks_per_row = p.k >> 3, total = p.m * chunks_per_row;
-            for (int c0 = et; c0 < ((total + 31) & ~31); c0 += 4 * 128) {  // four loads in flight per thread
-                float v[4][8];
-                int tok[4], ch[4];
-                bool valid[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int c = c0 + u * 128;
-                    tok[u] = c / chunks_per_row;
-                    ch[u] = c - tok[u] * chunks_per_row;
-                    valid[u] = c < total;
-                    load_act8(A.x, p.x_dtype, (int64_t)tok[u] * A.ldx + ch[u] * 8, valid[u], v[u]);
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (c0 + u * 128 >= ((total + 31) & ~31)) break;  // warp-uniform
-                    int e;
-                    uint32_t lo, hi;
-                    act_quant8(v[u], e, lo, hi);
-                    if (valid[u]) {
-                        const int slab = ch[u] >> 4, c16 = (ch[u] & 15) >> 1, half = ch[u] & 1;
-                        *reinterpret_cast<uint2 *>(bq + slab * kBsFusedBBytes + tok[u] * 128 + ((c16 ^ tok[u]) << 4) + half * 8) = make_uint2(lo, hi);
-                        if ((ch[u] & 3) == 0) {
-                            const int kb = ch[u] >> 2;
-                            sfq[(kb >> 2) * kBsFusedAtomBytes + tok[u] * 16 + (kb & 3)] = (uint8_t)min(max(e + 127, 0), 255);
-                        }
-                    }
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA and the copy
-        }
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        const uint32_t seq = step_begin(X);
+        const uint32_t bank = seq & 1u;
         bs_epi_bar();
-        if (FUSED && et == 0) mbar_arrive(xready);
         const int kofs = (int)(A.k0 - kcol0 * ((int64_t)1 << p.bk_shift));
         const bool solo = p.mode == kModeAllReduce && p.world == 1;
         const size_t astride = (size_t)p.lay.max_m * p.lay.max_n;
@@ -504,14 +503,14 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
             }
         };
 
-        BsWalk w(ntiles, cta, ncta, KS, SL);
+        BsWalk w(ntiles, part, nparts, k_lo, k_hi, SL);
         RingPos st, ag;  // stage ring, accumulator-group ring
         bool ok = true;
-        int tile, s0, nsl;
+        int tile, s0, nsl, ntile_done = 0;
         float acc[MP];
         const float *swrow = sw_s;
         while (w.next(tile, s0, nsl)) {
-            if (s0 == 0) {  // a new tile
+            if (s0 == k_lo) {  // a new tile
 #pragma unroll
                 for (int i = 0; i < MP; ++i) acc[i] = 0.0f;
                 const int row = min(tile * TR + min(rc, TR - 1), p.n - 1);
@@ -535,7 +534,29 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
             if (lane == 0) mbar_arrive(accempty0 + g * 8);
             st.next(NS);
             ag.next(NB);
-            if (s0 + nsl == KS) finalize(acc, tile);  // the tile's rows are final
+            if (s0 + nsl == k_hi) {  // this CTA's slabs of the tile are done
+                if (p.csize == 1) {
+                    finalize(acc, tile);
+                } else if (crank == 1) {
+                    // second CTA of the pair: hand the sums to the first one, into its shared memory
+                    if (ntile_done > 0) mbar_wait_cluster(rxempty, (uint32_t)(ntile_done - 1) & 1u, X.status);  // the previous tile's have been read
+                    const uint32_t dst = mapa_u32(smem_u32(smem + S.rx) + (uint32_t)rc * 4u, 0u);
+#pragma unroll
+                    for (int t = 0; t < MP; ++t)
+                        if (t < p.m) st_cluster_f32(dst + (uint32_t)(t * kBsMmaRows * 4), acc[t]);
+                    mbar_arrive_cluster(mapa_u32(rxfull, 0u));
+                } else {
+                    // first CTA: K half 0 (own) + K half 1 (the partner's), in that order
+                    mbar_wait_cluster(rxfull, (uint32_t)ntile_done & 1u, X.status);
+                    const float *rx = reinterpret_cast<const float *>(smem + S.rx) + rc;
+#pragma unroll
+                    for (int t = 0; t < MP; ++t)
+                        if (t < p.m) acc[t] += rx[t * kBsMmaRows];
+                    mbar_arrive_cluster(mapa_u32(rxempty, 1u));
+                    finalize(acc, tile);
+                }
+                ++ntile_done;
+            }
         }
 
         // ---- exchange (the 128 epilogue threads)
@@ -544,7 +565,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
         if (!solo && p.mode == kModeAllReduce) {
             // fold the rows of the tiles this CTA finished, in rank order, as the ranks' words arrive
             const uint64_t *slots = reinterpret_cast<const uint64_t *>(X.sym[X.rank] + p.lay.slota_off) + (size_t)bank * p.world * astride;
-            for (int t = t_lo; t <= t_hi; ++t) {
+            for (int t = t_lo; t <= t_hi && crank == 0; ++t) {  // in a pair the first CTA finished the tiles
                 const int row = t * TR + rc;
                 if (rc >= TR || row >= p.n) continue;
                 for (int tok = 0; tok < p.m; ++tok) {
@@ -682,6 +703,10 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
     // ---- teardown: every TMEM read and MMA has completed once all threads are here
     tc_fence_before();
     __syncthreads();
+    if (p.csize == 2) {  // neither CTA of a pair leaves while the other may still write to or signal it
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kBsTmemCols);
