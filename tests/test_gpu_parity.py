@@ -551,6 +551,27 @@ def test_oproj_full_size_64_rows(dev, tpmod, oracle):
         ep.close()
 
 
+@pytest.mark.parametrize("m", [1, 3])
+def test_vocab_sized_shard_values_on_the_tensor_memory_kernel(dev, tpmod, oracle, m):
+    """W FP8 [129280, 7168] through the all-reduce entry point on one rank: every CTA of the tcgen05
+    kernel walks seven row tiles of 125 rows, and every output row is compared with the oracle (the
+    lm_head form of the same launch leaves only the argmax)."""
+    from weightstream_b200 import synth
+    n, k = 129280, 7168
+    wd, sd = synth.torch_fp8_weight(n, k, seed=synth.config_seed("vocab_shard", m, 1), device=dev)
+    x = torch_bf16((m, k), 71 + m, dev)
+    ep = tpmod.Endpoint(max_m=8, max_n=n)
+    try:
+        ep.set_kernel(2)
+        got = ep.fp8_rowpar_gemm_allreduce(x, wd, sd).cpu().numpy()
+        ep.check()
+        want = oracle.fp8_gemv(wd.cpu().numpy(), sd.cpu().numpy(), bf16_to_f32_host(x), bn=128, bk=128, threads=oracle.max_threads())
+        err = rel_l2(got, want)
+        assert err <= REL_L2_TOL and err < 5e-5, err
+    finally:
+        ep.close()
+
+
 @pytest.mark.parametrize("m", [1, 2])
 def test_lm_head_full_size(dev, tpmod, oracle, m):
     """lm_head at the measured size, W FP8 [129280, 7168]: logits against the oracle, argmax equal to

@@ -493,7 +493,6 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
     for (int i = 0; i < n; ++i) {
         ws_tp *t = ranks[i];
         const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
-        if (lm && lm[i].logits) p.gather_logits = 1;
         ws_status_t s = ensure_bs_scratch(t, xq_bytes + sf_bytes);
         if (s == WS_OK) s = make_tmap(t, &p.tmap_w[i], a.w, (uint64_t)a.n, (uint64_t)a.k, (uint64_t)a.ldw, (uint32_t)u.tile_rows);
         uint8_t *const xq = t->bs_work;
@@ -504,7 +503,7 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
         r.x = nullptr;
         r.scales = a.scales;
         r.out = lm ? nullptr : a.out + (size_t)m0 * a.n;
-        r.logits = lm && lm[i].logits ? lm[i].logits + (size_t)m0 * lm[i].vocab : nullptr;
+        r.logits = nullptr;
         r.argmax = lm && lm[i].argmax ? lm[i].argmax + m0 : nullptr;
         r.ldx = a.ldx; r.scale_ld = a.scale_ld; r.row0 = a.row0; r.k0 = a.k0;
         r.vocab_row0 = lm ? lm[i].vocab_row0 : 0;
@@ -544,22 +543,25 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
 
 // Whether rows [.., +mt) of this step go to the block-scaled tcgen05 path: always when the caller
 // selected it; by default from three rows up, and for one or two rows when the shard is large enough
-// for its streaming rate to outweigh the second launch (measured on B200, M=1: 58.7 MB 16.4 us against
-// 17.2 us on CUDA cores, 927 MB 153 against 208 us; 14.7 MB 8.8 against 6.8 us, 7.3 MB 12.8 against 5.9 us).
-static bool bs_wanted(const ws_tp *t0, int mt, const ws_fp8_gemm_args_t &a) {
+// for its streaming rate to outweigh the second launch (measured on B200, M=1: 927 MB 153 against
+// 208 us on CUDA cores; 58.7 MB 17.7 against 17.2 us, 14.7 MB 8.8 against 6.8 us, 7.3 MB 12.8 against 5.9 us).
+// A step that also gathers the logits stays on the CUDA-core kernel: the tensor-memory kernel leaves
+// only the argmax candidates (the decode loop's form of the call).
+static bool bs_wanted(const ws_tp *t0, int mt, const ws_fp8_gemm_args_t &a, bool gathers_logits) {
+    if (gathers_logits) return false;
     if (t0->kernel_sel == 2) return true;
     if (t0->kernel_sel != 0) return false;
-    return mt >= 3 || (int64_t)a.n * a.k >= ((int64_t)32 << 20);
+    return mt >= 3 || (int64_t)a.n * a.k >= ((int64_t)128 << 20);
 }
 
 // Activation rows the next launch takes: up to 64 when their quantised copies fit in shared
 // memory beside at least three weight stages (the weights are then streamed once for all of
 // them), else 8.
-static int fp8_rows_per_launch(const ws_tp *t0, const ws_fp8_gemm_args_t &a, int ncta, int rem) {
+static int fp8_rows_per_launch(const ws_tp *t0, const ws_fp8_gemm_args_t &a, int ncta, int rem, bool gathers_logits) {
     {   // the tensor-memory path streams the weights once for up to 64 rows
         const int mt = std::min(rem, (int)kBsMaxTokens);
         const int skb = (int)((a.k0 + a.k - 1) / a.block_k - a.k0 / a.block_k + 1);
-        if (bs_wanted(t0, mt, a) && bs_plan(a, mt, skb, ncta, false).ok) return mt;
+        if (bs_wanted(t0, mt, a, gathers_logits) && bs_plan(a, mt, skb, ncta, false).ok) return mt;
     }
     if (rem <= 8) return rem;
     const int kbox = (a.k + 127) / 128;
@@ -578,7 +580,9 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
                             int m0, int mt, void *const *streams, int ncta, bool same_device) {
     ws_tp *t0 = ranks[0];
     const ws_fp8_gemm_args_t &a0 = lm ? lm[0].g : args[0];
-    if (bs_wanted(t0, mt, a0)) {  // tensor-memory path whenever the shape fits it
+    bool gathers_logits = false;
+    for (int i = 0; lm && i < n; ++i) gathers_logits |= lm[i].logits != nullptr;
+    if (bs_wanted(t0, mt, a0, gathers_logits)) {  // tensor-memory path whenever the shape fits it
         int64_t skb_u = 1;
         for (int i = 0; i < n; ++i) {
             const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
@@ -688,7 +692,7 @@ ws_status_t ws_fp8_rowpar_gemm_allreduce_group(ws_tp_t *const *ranks, int32_t n,
         return fail(t0, WS_ERR_CAPACITY, "m=%d n=%d exceed the endpoint's max_m=%d max_n=%d", args[0].m, args[0].n,
                     t0->cfg.max_m, t0->cfg.max_n);
     for (int m0 = 0; m0 < args[0].m;) {
-        const int mt = fp8_rows_per_launch(t0, args[0], ncta, args[0].m - m0);
+        const int mt = fp8_rows_per_launch(t0, args[0], ncta, args[0].m - m0, false);
         s = fp8_step(ranks, n, args, nullptr, m0, mt, streams, ncta, same);
         if (s != WS_OK) return s;
         m0 += mt;
@@ -727,7 +731,7 @@ ws_status_t ws_lm_head_allgather_argmax_group(ws_tp_t *const *ranks, int32_t n, 
     if (any_logits && args[0].vocab > t0->cfg.max_vocab)
         return fail(t0, WS_ERR_CAPACITY, "vocab=%d exceeds the endpoint's max_vocab=%d", args[0].vocab, t0->cfg.max_vocab);
     for (int m0 = 0; m0 < args[0].g.m;) {
-        const int mt = fp8_rows_per_launch(t0, args[0].g, ncta, args[0].g.m - m0);
+        const int mt = fp8_rows_per_launch(t0, args[0].g, ncta, args[0].g.m - m0, any_logits);
         s = fp8_step(ranks, n, nullptr, args, m0, mt, streams, ncta, same);
         if (s != WS_OK) return s;
         m0 += mt;

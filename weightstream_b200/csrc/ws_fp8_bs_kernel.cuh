@@ -31,7 +31,7 @@
 //
 // MMA rows past a tile's end are computed on whatever follows in shared memory and never read back.
 // Exchange and lm_head mode are those of the decode kernel (ws_fp8_kernel.cuh): tagged 64-bit
-// words stored into every peer's slots and folded in rank order, or gather + argmax candidates.
+// words stored into every peer's slots and folded in rank order, or argmax candidates merged per rank.
 #pragma once
 
 #include <math.h>
@@ -41,7 +41,7 @@
 
 namespace ws {
 
-constexpr int kBsThreads = 224;      // warp 0: producer, warps 1 and 6: MMA issue (warp 1 owns TMEM), warps 2-5: epilogue
+constexpr int kBsThreads = 192;      // warp 0: producer, warp 1: MMA issue (and owner of the tensor memory), warps 2-5: epilogue
 constexpr int kBsTmemCols = 512;
 constexpr int kBsMaxAcc = 8;         // accumulator groups in tensor memory (a group = one stage's slabs)
 constexpr int kBsMaxTokens = 64;     // activation rows one launch takes
@@ -93,7 +93,7 @@ struct alignas(64) BsParams {
     CUtensorMap tmap_w[WS_MAX_WORLD];  // weight shard [n][k bytes], box 128 bytes x tile_rows, 128B swizzle
     CUtensorMap tmap_x[WS_MAX_WORLD];  // quantised activations [mp][k bytes], box 128 bytes x mp, 128B swizzle
     int32_t m, mp, n, k, bn_shift, bk_shift;
-    int32_t world, mode, vocab, gather_logits;
+    int32_t world, mode, vocab, pad1;
     int32_t pad0;
     int32_t csize;                     // 1, or 2: CTA pairs (a cluster) share a tile, each streams half of K
     int32_t tile_rows, ntiles;         // output rows per tile (<= 128) and tiles of the shard
@@ -328,7 +328,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
         tmem_alloc(smem_u32(misc_s), kBsTmemCols);
         tmem_relinquish();
     }
-    if (warp >= 2 && warp < 6) {  // the weight operand's scale atom: 2^0 everywhere (128 threads x 4 bytes)
+    if (warp >= 2) {  // the weight operand's scale atom: 2^0 everywhere (128 threads x 4 bytes)
         uint32_t *sfa = reinterpret_cast<uint32_t *>(smem + S.sfa);
         sfa[tid - 64] = 0x7F7F7F7Fu;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -342,9 +342,9 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
     }
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(misc_s);
     // tensor-memory columns: NB groups x SL accumulator buffers of MP columns, then 4 activation-scale
-    // columns (one scale atom) per buffer, then 4 weight-scale columns for each of the two issuing threads
+    // columns (one scale atom) per buffer, then the 4 weight-scale columns
     const uint32_t t_sfb0 = tmem_base + (uint32_t)(NB * SL * MP);
-    const uint32_t t_sfa0 = t_sfb0 + (uint32_t)(NB * SL * 4);
+    const uint32_t t_sfa = t_sfb0 + (uint32_t)(NB * SL * 4);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
@@ -383,16 +383,15 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
                 issue_x(s, s0, nsl);
             }
         }
-    } else if (warp == 1 || warp == 6) {
-        // ------------------------------------------------------------ MMA issue (one thread of each warp)
-        // Two threads take the stage items in turn.  Issuing an MMA holds its thread for about as long
-        // as the tensor pipe needs for it, and every item costs a few hundred ns of waits and a commit:
-        // with two issuers one thread's bookkeeping runs while the other's MMAs execute.  Items go to
-        // different stages and accumulator groups, so the two never touch the same memory.
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issue (one thread)
+        // A second issuing thread (stage items taken in turn, so that one thread's waits and commit hide
+        // behind the other's MMAs) was ~7% faster on one-row steps, but a launch that streamed a
+        // [129280, 7168] shard partly out of L2 (weights written just before) then ended in "unspecified
+        // launch failure" in most attempts, in a different CTA and stage item each time, and never with
+        // one thread; the barrier hand-offs are the same either way, so the cause is not known.
         asm volatile("griddepcontrol.wait;" ::: "memory");
         if (lane == 0) {
-            const int mine = warp == 6 ? 1 : 0;
-            const uint32_t t_sfa = t_sfa0 + (uint32_t)(mine * 4);  // own copy: a copy and the MMAs that read it are ordered only within one thread
             tmem_cp_atom(t_sfa, umma_desc(smem_u32(smem + S.sfa), 128, false));
             // Everything the loop needs per MMA is an add away: descriptor halves per stage slot, the
             // four instruction descriptors (one per K block of a slab), ring positions kept incrementally.
@@ -405,7 +404,6 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
             RingPos st, ag;  // stage ring, accumulator-group ring
             int tile, s0, nsl;
             for (int item = 0; w.next(tile, s0, nsl); ++item, st.next(NS), ag.next(NB)) {
-                if ((item & 1) != mine) continue;
                 const int s = st.s, g = ag.s;
                 if (!mbar_wait(full0 + s * 8, st.ph, X.status) || !mbar_wait(accempty0 + g * 8, ag.ph ^ 1u, X.status)) break;
                 tc_fence_after();
@@ -456,7 +454,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
         if (p.mode == kModeLmHead)
             for (int i = lane; i < MP; i += 32) { cv_s[(warp - 2) * MP + i] = -INFINITY; ci_s[(warp - 2) * MP + i] = 0xFFFFFFFFu; }
 
-        // A finished tile: its rows go to the output, to the peers, or to the gather and the candidates.
+        // A finished tile: its rows go to the output or to the peers; of an lm_head tile the candidates are kept.
         auto finalize = [&](const float (&v)[MP], int tile) {
             const int row = tile * TR + rc;
             const bool mine = rc < TR && row < p.n;
@@ -471,13 +469,6 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
 #pragma unroll
                         for (int t = 0; t < MP; ++t)
                             if (t < p.m) st_word_sys(dst + (size_t)t * p.n + row, seq, v[t]);
-                    }
-                } else if (p.gather_logits) {
-                    for (int pr = 0; pr < p.world; ++pr) {
-                        float *dst = reinterpret_cast<float *>(X.sym[pr] + p.lay.gather_off) + (size_t)bank * p.lay.max_m * (size_t)p.lay.max_vocab;
-#pragma unroll
-                        for (int t = 0; t < MP; ++t)
-                            if (t < p.m) dst[(size_t)t * p.lay.max_vocab + A.vocab_row0 + row] = v[t];
                     }
                 }
             }
@@ -576,7 +567,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
                     A.out[off] = s;
                 }
             }
-        } else if (p.mode == kModeLmHead && !p.gather_logits) {
+        } else if (p.mode == kModeLmHead) {
             // Only the argmax is wanted.  The CTAs of a rank leave their candidates in the rank's own
             // table; the CTA that arrives last merges them into ONE (value, lowest index) per token,
             // sends it to every peer and merges the ranks' candidates: one 64-bit store and one flag
@@ -641,61 +632,6 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
                         const uint64_t best = merge(t, p.world, [&](int i) { return table + ((size_t)i * kMaxCtas + kRankRow) * p.lay.max_m; });
                         if (lane == 0) A.argmax[t] = ((uint32_t)best == 0xFFFFFFFFu) ? 0u : (uint32_t)best;
                     }
-            }
-        } else if (p.mode == kModeLmHead) {
-            bs_epi_bar();
-            if (et < p.m) {  // this CTA's candidate per token -> every peer's candidate table
-                float bv = cv_s[et];
-                uint32_t bi = ci_s[et];
-                for (int w = 1; w < 4; ++w)
-                    if (cand_better(cv_s[w * MP + et], ci_s[w * MP + et], bv, bi)) { bv = cv_s[w * MP + et]; bi = ci_s[w * MP + et]; }
-                for (int pr = 0; pr < p.world; ++pr) {
-                    uint64_t *dst = reinterpret_cast<uint64_t *>(X.sym[pr] + p.lay.pairs_off) +
-                                    (((size_t)bank * p.world + X.rank) * kMaxCtas + cta) * p.lay.max_m + et;
-                    *dst = ((uint64_t)__float_as_uint(bv) << 32) | bi;
-                }
-            }
-            bs_epi_bar();  // the st.release.sys below is cumulative over the stores this barrier ordered
-            if (et < p.world) {
-                uint32_t *f = reinterpret_cast<uint32_t *>(X.sym[et] + p.lay.flags_off) + ((size_t)bank * p.world + X.rank) * nflag;
-                st_release_sys(f + cta, seq);
-            }
-            const bool copies = p.gather_logits && A.logits != nullptr;
-            if (copies || cta == 0) {
-                // every CTA of every rank has published (its flag follows all of its stores)
-                for (int i = et; i < p.world * ncta; i += 128)
-                    wait_flag(myflags + (size_t)(i / ncta) * nflag + (i % ncta), seq, p.timeout_ns, X.status, kStatTimeoutGather);
-                bs_epi_bar();
-                if (copies) {
-                    const float *gl = reinterpret_cast<const float *>(X.sym[X.rank] + p.lay.gather_off) +
-                                      (size_t)bank * p.lay.max_m * (size_t)p.lay.max_vocab;
-                    const int64_t per = ((int64_t)p.vocab + ncta - 1) / ncta;
-                    const int64_t v0 = (int64_t)cta * per, v1 = min((int64_t)p.vocab, v0 + per);
-                    for (int t = 0; t < p.m; ++t)
-                        for (int64_t v = v0 + et; v < v1; v += 128)
-                            A.logits[(size_t)t * p.vocab + v] = __ldcg(gl + (size_t)t * p.lay.max_vocab + v);
-                }
-                if (cta == 0 && A.argmax != nullptr) {
-                    const uint64_t *pairs = reinterpret_cast<const uint64_t *>(X.sym[X.rank] + p.lay.pairs_off) +
-                                            (size_t)bank * p.world * kMaxCtas * p.lay.max_m;
-                    for (int t = warp - 2; t < p.m; t += 4) {
-                        float bv = -INFINITY;
-                        uint32_t bi = 0xFFFFFFFFu;
-                        for (int i = lane; i < p.world * ncta; i += 32) {
-                            const uint64_t pr = ld_volatile_u64(pairs + ((size_t)(i / ncta) * kMaxCtas + (i % ncta)) * p.lay.max_m + t);
-                            const float v = __uint_as_float((uint32_t)(pr >> 32));
-                            const uint32_t idx = (uint32_t)pr;
-                            if (cand_better(v, idx, bv, bi)) { bv = v; bi = idx; }
-                        }
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) {
-                            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                            if (cand_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-                        }
-                        if (lane == 0) A.argmax[t] = (bi == 0xFFFFFFFFu) ? 0u : bi;
-                    }
-                }
             }
         }
     }
