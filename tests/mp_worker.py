@@ -31,13 +31,13 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     sh = tp.Sharding(world, rank)
     vocab = 16 * 101 * world
-    ep = tp.Endpoint(sh, lr, max_m=16, max_n=7168, max_vocab=vocab, wait_ms=5000)
+    ep = tp.Endpoint(sh, lr, max_m=64, max_n=7168, max_vocab=vocab, wait_ms=5000)
     ep.connect_process_group()
     rng = np.random.default_rng(7)  # same tensors on every rank
     # o_proj, K sliced
     n, k = 7168, 2048
     w, sc = synth.fp8_weight(rng, n, k)
-    for m in (1, 11):
+    for m in (1, 11, 40):  # 11 and 40 rows run on the tcgen05 kernel (CTA pairs sending tagged words to every rank)
         xb = synth.activations_bf16(rng, m, k)
         xf = F.bf16_bits_to_f32(xb)
         k0, kl = sh.slice_of(k)
@@ -89,6 +89,16 @@ def main():
     assert rel(logits.cpu().numpy(), lw) < 5e-5, "lm_head"
     assert [int(a) for a in am.cpu()] == [O.argmax(lw[t]) for t in range(2)]
     assert same_everywhere(logits, world)
+    # the decode form: argmax only (one merged candidate per rank crosses the links), 1 row and 40 rows
+    for m in (2, 40):
+        xm = synth.activations_bf16(rng, m, 512)
+        _, am2 = ep.lm_head_allgather_argmax(torch.from_numpy(xm.view(np.int16)).to(dev).view(torch.bfloat16),
+                                             torch.from_numpy(wv[v0:v0 + vl]).to(dev), s_r.contiguous(),
+                                             vocab_row0=v0, vocab=vocab, row0=row0, want_logits=False)
+        ep.check()
+        lm = O.fp8_gemv(wv, sv, F.bf16_bits_to_f32(xm), bn=128, bk=128, threads=4)
+        assert [int(a) for a in am2.cpu()] == [O.argmax(lm[t]) for t in range(m)], f"argmax-only lm_head m={m}"
+        assert same_everywhere(am2, world)
     ep.close()
     dist.barrier()
     if rank == 0:

@@ -53,7 +53,8 @@ struct ws_tp {
         cudaGraphExec_t exec = nullptr;
     };
     std::unordered_map<uint64_t, HostGraph> hgraphs;  // keyed by a hash of the argument set
-    uint32_t *pin_status = nullptr;
+    uint64_t *pin_done = nullptr;       // pinned: {1, device status} once a host-buffer call's last kernel has finished
+    uint64_t *host_done_arm = nullptr;  // set while a host-buffer call enqueues: its last kernel reports to this word
     uint64_t hgraph_clock = 0;
     // MoE decode step: routes quantised once per step, pass table, large-m accumulators
     uint8_t *moe_work = nullptr;
@@ -157,6 +158,7 @@ RankCtx make_ctx(const ws_tp *tp) {
     c.status = tp->status;
     c.step_ctr = tp->counters + kMaxShared + 2;
     c.rank = tp->rank;
+    c.host_done = nullptr;
     return c;
 }
 
@@ -273,7 +275,12 @@ ws_status_t ws_tp_create(int32_t world, int32_t rank, int32_t device, const ws_t
     if (set_smem(tp, moe_gemv_kernel) != WS_OK || set_smem(tp, fp8_rowpar_kernel<0>) != WS_OK || set_smem(tp, fp8_rowpar_kernel<1>) != WS_OK ||
         set_smem(tp, fp8_rowpar_kernel<2>) != WS_OK || set_smem(tp, moe_down_kernel) != WS_OK ||
         set_smem(tp, fp8_bs_kernel<16>) != WS_OK || set_smem(tp, fp8_bs_kernel<32>) != WS_OK ||
-        set_smem(tp, fp8_bs_kernel<64>) != WS_OK)
+        set_smem(tp, fp8_bs_kernel<64>) != WS_OK ||
+        // The prep kernel uses no shared memory, but a main-kernel CTA (which needs almost all of an SM's)
+        // cannot move onto an SM whose L1/shared split must first change, and that has to wait for the prep
+        // blocks there to leave: measured 2.5-4.5 us of late CTAs.  With the same preference nothing changes.
+        cudaFuncSetAttribute(act_prep_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
+        cudaFuncSetAttribute(stage_in_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
         return bail(WS_ERR_CUDA);
     *out = tp;
     return WS_OK;
@@ -289,7 +296,7 @@ ws_status_t ws_tp_destroy(ws_tp_t *tp) {
     if (tp->dev_stage) cudaFree(tp->dev_stage);
     for (auto &g : tp->hgraphs)
         if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
-    if (tp->pin_status) cudaFreeHost(tp->pin_status);
+    if (tp->pin_done) cudaFreeHost(tp->pin_done);
     if (tp->moe_work) cudaFree(tp->moe_work);
     if (tp->moe_acc) cudaFree(tp->moe_acc);
     if (tp->bs_work) cudaFree(tp->bs_work);
@@ -470,7 +477,7 @@ static ws_status_t ensure_bs_scratch(ws_tp *tp, size_t bytes) {
 // One fused step over at most 64 activation rows on the block-scaled tcgen05 path: the prep
 // kernel (activation quantisation once per step) followed by the persistent MMA kernel.
 static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t *args, const ws_lm_head_args_t *lm,
-                           int m0, int mt, void *const *streams, int ncta, bool same_device, const BsPlan &u, int skb) {
+                           int m0, int mt, void *const *streams, int ncta, bool same_device, const BsPlan &u, int skb, bool last) {
     ws_tp *t0 = ranks[0];
     const ws_fp8_gemm_args_t &a0 = lm ? lm[0].g : args[0];
     BsParams p{};
@@ -508,6 +515,7 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
         r.ldx = a.ldx; r.scale_ld = a.scale_ld; r.row0 = a.row0; r.k0 = a.k0;
         r.vocab_row0 = lm ? lm[i].vocab_row0 : 0;
         r.ctx = make_ctx(t);
+        if (last) r.ctx.host_done = t->host_done_arm;
         p.sfb[i] = xq + xq_bytes;
         q.r[i].x = static_cast<const char *>(a.x) + (size_t)m0 * a.ldx * xes;
         q.r[i].xq = xq;
@@ -577,7 +585,7 @@ static int fp8_rows_per_launch(const ws_tp *t0, const ws_fp8_gemm_args_t &a, int
 
 // One fused step over the activation rows [m0, m0 + mt) (mt from fp8_rows_per_launch).
 static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t *args, const ws_lm_head_args_t *lm,
-                            int m0, int mt, void *const *streams, int ncta, bool same_device) {
+                            int m0, int mt, void *const *streams, int ncta, bool same_device, bool last) {
     ws_tp *t0 = ranks[0];
     const ws_fp8_gemm_args_t &a0 = lm ? lm[0].g : args[0];
     bool gathers_logits = false;
@@ -589,7 +597,7 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
             skb_u = std::max<int64_t>(skb_u, (a.k0 + a.k - 1) / a.block_k - a.k0 / a.block_k + 1);
         }
         const BsPlan u = bs_plan(a0, mt, (int)skb_u, ncta, n == 1);  // CTA pairs need a cluster launch, virtual ranks a cooperative one
-        if (u.ok) return bs_step(ranks, n, args, lm, m0, mt, streams, ncta, same_device, u, (int)skb_u);
+        if (u.ok) return bs_step(ranks, n, args, lm, m0, mt, streams, ncta, same_device, u, (int)skb_u, last);
     }
     Fp8Params p{};
     p.m = mt; p.n = a0.n; p.k = a0.k; p.x_dtype = a0.x_dtype; p.scale_kind = a0.scale_kind;
@@ -646,6 +654,7 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
         r.ldx = a.ldx; r.scale_ld = a.scale_ld; r.row0 = a.row0; r.k0 = a.k0;
         r.vocab_row0 = lm ? lm[i].vocab_row0 : 0;
         r.ctx = make_ctx(t);
+        if (last) r.ctx.host_done = t->host_done_arm;
         p.w[i] = a.w;
         p.ldw[i] = a.ldw;
     }
@@ -693,7 +702,7 @@ ws_status_t ws_fp8_rowpar_gemm_allreduce_group(ws_tp_t *const *ranks, int32_t n,
                     t0->cfg.max_m, t0->cfg.max_n);
     for (int m0 = 0; m0 < args[0].m;) {
         const int mt = fp8_rows_per_launch(t0, args[0], ncta, args[0].m - m0, false);
-        s = fp8_step(ranks, n, args, nullptr, m0, mt, streams, ncta, same);
+        s = fp8_step(ranks, n, args, nullptr, m0, mt, streams, ncta, same, m0 + mt >= args[0].m);
         if (s != WS_OK) return s;
         m0 += mt;
     }
@@ -732,7 +741,7 @@ ws_status_t ws_lm_head_allgather_argmax_group(ws_tp_t *const *ranks, int32_t n, 
         return fail(t0, WS_ERR_CAPACITY, "vocab=%d exceeds the endpoint's max_vocab=%d", args[0].vocab, t0->cfg.max_vocab);
     for (int m0 = 0; m0 < args[0].g.m;) {
         const int mt = fp8_rows_per_launch(t0, args[0].g, ncta, args[0].g.m - m0, any_logits);
-        s = fp8_step(ranks, n, nullptr, args, m0, mt, streams, ncta, same);
+        s = fp8_step(ranks, n, nullptr, args, m0, mt, streams, ncta, same, m0 + mt >= args[0].g.m);
         if (s != WS_OK) return s;
         m0 += mt;
     }
@@ -1071,18 +1080,74 @@ static bool same_fp8_args(const ws_fp8_gemm_args_t &a, const ws_fp8_gemm_args_t 
            a.block_k == b.block_k && a.row0 == b.row0 && a.k0 == b.k0;
 }
 
+// Activations of a host-buffer call on their way in: nothing to do when the step's own prep kernel
+// reads the pinned buffer, a fetching kernel for small inputs, the copy engine for large ones.
+static bool host_stage_in(ws_tp *tp, char *dev, const char *pin, size_t bytes, bool direct, bool stage) {
+    if (direct && !stage) return true;
+    if (!direct) return cudaMemcpyAsync(dev, pin, bytes, cudaMemcpyHostToDevice, tp->hstream) == cudaSuccess;
+    StageParams q{reinterpret_cast<const uint4 *>(pin), reinterpret_cast<uint4 *>(dev), (int64_t)((bytes + 15) / 16)};
+    const int blocks = (int)((q.n16 + 255) / 256);
+    return launch(tp, stage_in_kernel, q, blocks, 1, 256, 0, tp->hstream, tp->pdl != 0, false) == WS_OK;
+}
+
+// Wait for the word the step's last kernel sets in pinned memory, then hand the results (which the
+// kernel wrote into the pinned buffer) to the caller.  The stream is asked now and then, so that a
+// launch that died, or a step that ended without reporting, still ends the call.
+static ws_status_t host_wait_and_copy_out(ws_tp *tp, volatile uint64_t *done, float *out_host, const char *src, size_t bytes) {
+    uint64_t word = 0;
+    for (uint32_t spins = 0; (word = *done) == 0; ++spins) {
+        if ((spins & 0xFFFu) == 0xFFFu) {
+            if (cudaStreamQuery(tp->hstream) == cudaErrorNotReady) continue;
+            word = *done;  // the stream has drained (or died): whatever the kernel wrote is there now
+            break;
+        }
+#if defined(__x86_64__)
+        __builtin_ia32_pause();
+#endif
+    }
+    if (word == 0 || (uint32_t)word != 0u) {  // no report, or a device code: the check turns it into status + message
+        const ws_status_t s = ws_tp_check(tp, tp->hstream);
+        if (s != WS_OK) return s;
+    }
+    memcpy(out_host, src, bytes);
+    return WS_OK;
+}
+
 ws_status_t ws_fp8_rowpar_gemm_allreduce_host(ws_tp_t *tp, const ws_fp8_gemm_args_t *dw, const void *x_host, float *out_host) {
     if (!tp || !dw || !x_host || !out_host) return WS_ERR_INVALID;
     const size_t es = dw->x_dtype == WS_ACT_BF16 ? 2 : 4;
     const size_t xb = (size_t)dw->m * dw->k * es, xb_al = (xb + 255) / 256 * 256, ob = (size_t)dw->m * dw->n * 4;
-    ws_status_t s = ensure_staging(tp, xb_al + ob, xb_al + ob);
+    ws_status_t s = ensure_staging(tp, xb_al + ob, xb_al);
     if (s != WS_OK) return s;
-    if (!tp->pin_status) WS_CUDA(tp, cudaHostAlloc(reinterpret_cast<void **>(&tp->pin_status), 64, cudaHostAllocDefault));
+    if (!tp->pin_done) WS_CUDA(tp, cudaHostAlloc(reinterpret_cast<void **>(&tp->pin_done), 64, cudaHostAllocDefault));
     char *pin = static_cast<char *>(tp->pin), *dev = static_cast<char *>(tp->dev_stage);
+    // The activations are copied in; the results are written by the kernel straight into the pinned
+    // buffer (it is mapped into the device's address space), and the last CTA sets *pin_done: no copy
+    // back and no wait on the stream stand between the last store and the host.
     ws_fp8_gemm_args_t a = *dw;
     a.x = dev;
     a.ldx = dw->k;
-    a.out = reinterpret_cast<float *>(dev + xb_al);
+    a.out = reinterpret_cast<float *>(pin + xb_al);
+    volatile uint64_t *done = tp->pin_done;
+
+    // Up to 64 KB of activations: no copy engine on the way in either.  A kernel fetches them from the
+    // pinned buffer over PCIe (a few us for 16 KB) while the main kernel, launched with it from one graph
+    // and already resident, streams its first weights: the tensor-memory path's prep kernel reads them in
+    // place; for the CUDA-core path a small kernel brings them into device memory.  Either way the step
+    // runs on the kernel a device-buffer call with these arguments runs on, so the results are the same bits.
+    bool direct = false, stage = false;
+    if (xb <= 64 * 1024) {
+        int ncta = 0;
+        bool same = true;
+        ws_tp *self[1] = {tp};
+        if (validate_fp8(tp, a, false) == WS_OK && group_prelude(self, 1, &ncta, &same) == WS_OK) {
+            const int skb = (int)((dw->k0 + dw->k - 1) / dw->block_k - dw->k0 / dw->block_k + 1);
+            const int mt = fp8_rows_per_launch(tp, a, ncta, a.m, false);
+            direct = true;
+            stage = !(bs_wanted(tp, mt, a, false) && bs_plan(a, mt, skb, ncta, true).ok);
+            if (!stage) a.x = pin;
+        }
+    }
 
     ws_tp::HostGraph *hit = nullptr;
     const uint64_t hkey = hash_fp8_args(a, pin, dev, tp->kernel_sel * 4 + tp->split * 2 + tp->pdl);
@@ -1099,16 +1164,15 @@ ws_status_t ws_fp8_rowpar_gemm_allreduce_host(ws_tp_t *tp, const ws_fp8_gemm_arg
             }
         }
     }
+    tp->host_done_arm = tp->pin_done;
     if (!hit) {  // capture; any failure falls back to plain enqueueing below
         const uint64_t step0 = tp->step, launches0 = tp->launches;
         cudaGraph_t graph = nullptr;
         cudaGraphExec_t exec = nullptr;
         bool ok = cudaStreamBeginCapture(tp->hstream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
         if (ok) {
-            ok = cudaMemcpyAsync(dev, pin, xb, cudaMemcpyHostToDevice, tp->hstream) == cudaSuccess;
+            ok = host_stage_in(tp, dev, pin, xb, direct, stage);
             ok = ok && ws_fp8_rowpar_gemm_allreduce(tp, &a, tp->hstream) == WS_OK;
-            ok = ok && cudaMemcpyAsync(pin + xb_al, dev + xb_al, ob, cudaMemcpyDeviceToHost, tp->hstream) == cudaSuccess;
-            ok = ok && cudaMemcpyAsync(tp->pin_status, tp->status, sizeof(uint32_t), cudaMemcpyDeviceToHost, tp->hstream) == cudaSuccess;
             const bool ended = cudaStreamEndCapture(tp->hstream, &graph) == cudaSuccess && graph != nullptr;
             ok = ok && ended && cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
             if (graph) cudaGraphDestroy(graph);
@@ -1133,23 +1197,24 @@ ws_status_t ws_fp8_rowpar_gemm_allreduce_host(ws_tp_t *tp, const ws_fp8_gemm_arg
         }
     }
     memcpy(pin, x_host, xb);
+    *done = 0;
     if (hit) {
         hit->used = ++tp->hgraph_clock;
-        WS_CUDA(tp, cudaGraphLaunch(hit->exec, tp->hstream));
-        tp->step += hit->steps;
-        tp->launches += hit->launches;
-        WS_CUDA(tp, cudaStreamSynchronize(tp->hstream));
-        if (*tp->pin_status != 0u) return ws_tp_check(tp, tp->hstream);  // turns the device code into status + message
+        s = cudaGraphLaunch(hit->exec, tp->hstream) == cudaSuccess ? WS_OK : WS_ERR_CUDA;
+        if (s == WS_OK) {
+            tp->step += hit->steps;
+            tp->launches += hit->launches;
+        }
     } else {
-        WS_CUDA(tp, cudaMemcpyAsync(dev, pin, xb, cudaMemcpyHostToDevice, tp->hstream));
-        s = ws_fp8_rowpar_gemm_allreduce(tp, &a, tp->hstream);
-        if (s != WS_OK) return s;
-        WS_CUDA(tp, cudaMemcpyAsync(pin + xb_al, dev + xb_al, ob, cudaMemcpyDeviceToHost, tp->hstream));
-        s = ws_tp_check(tp, tp->hstream);
-        if (s != WS_OK) return s;
+        s = host_stage_in(tp, dev, pin, xb, direct, stage) ? WS_OK : WS_ERR_CUDA;
+        if (s == WS_OK) s = ws_fp8_rowpar_gemm_allreduce(tp, &a, tp->hstream);
     }
-    memcpy(out_host, pin + xb_al, ob);
-    return WS_OK;
+    tp->host_done_arm = nullptr;
+    if (s != WS_OK) {
+        if (s == WS_ERR_CUDA) return fail(tp, WS_ERR_CUDA, "enqueueing the host-buffer step failed: %s", cudaGetErrorString(cudaGetLastError()));
+        return s;
+    }
+    return host_wait_and_copy_out(tp, done, out_host, pin + xb_al, ob);
 }
 
 // ------------------------------------------------------------------------------ act quant

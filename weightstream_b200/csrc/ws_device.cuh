@@ -63,7 +63,8 @@ struct RankCtx {
     char *sym[WS_MAX_WORLD];  // sym[p] = rank p's exchange region as mapped here
     uint32_t *counters;       // local: [kMaxShared] arrival counters (self-resetting)
     uint32_t *status;         // local: first error wins
-    uint32_t *step_ctr;       // local: [0] steps completed by this rank, [1] CTAs done with the current step
+    uint32_t *step_ctr;       // local: [0] steps completed by this rank, [1] CTAs done with the current step, [2] CTAs that reported to the host
+    uint64_t *host_done;      // host-buffer calls: a word in pinned host memory the last CTA sets (see host_done_signal); else null
     int32_t rank;
     int32_t pad;
 };
@@ -352,6 +353,26 @@ __device__ __forceinline__ void step_end(const RankCtx &X, uint32_t seq, uint32_
             X.step_ctr[1] = 0u;
             __threadfence();
             *reinterpret_cast<volatile uint32_t *>(X.step_ctr) = seq;
+        }
+    }
+}
+
+// Host-buffer calls write their results straight into pinned host memory and the host waits on one
+// word there instead of on the stream.  Every CTA, once all of its threads have stored their results,
+// fences at system scope (its stores have then reached host memory: a PCIe round trip, ~3 us) and
+// counts itself in; the CTA that counts last stores {1, status word}.  That store is issued after every
+// CTA's fence has completed, so the host cannot see it before the results, and needs no second fence.
+__device__ __forceinline__ void host_done_signal(const RankCtx &X, uint32_t ncta) {
+    if (X.host_done == nullptr) return;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const uint32_t prev = atomicAdd(X.step_ctr + 2, 1u);
+        if (prev + 1u == ncta) {
+            X.step_ctr[2] = 0u;
+            __threadfence();  // the count is read before the word is written
+            const uint64_t word = ((uint64_t)1 << 32) | *reinterpret_cast<volatile uint32_t *>(X.status);
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(X.host_done), "l"(word) : "memory");
         }
     }
 }

@@ -559,12 +559,29 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
             for (int t = t_lo; t <= t_hi && crank == 0; ++t) {  // in a pair the first CTA finished the tiles
                 const int row = t * TR + rc;
                 if (rc >= TR || row >= p.n) continue;
-                for (int tok = 0; tok < p.m; ++tok) {
-                    const size_t off = (size_t)tok * p.n + row;
-                    float s = wait_word(slots + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-                    for (int rr = 1; rr < p.world; ++rr)
-                        s += wait_word(slots + rr * astride + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-                    A.out[off] = s;
+                // 16 tokens at a time: their words of one rank are all requested before the first is
+                // looked at (one memory round trip per batch, not per word); a word that has not
+                // arrived yet is then waited for on its own.  Ranks are added in rank order.
+                for (int tok0 = 0; tok0 < p.m; tok0 += 16) {
+                    float sum[16];
+                    for (int rr = 0; rr < p.world; ++rr) {
+                        const uint64_t *src = slots + rr * astride + (size_t)tok0 * p.n + row;
+                        uint64_t w[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (tok0 + i < p.m) w[i] = ld_word_sys(src + (size_t)i * p.n);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (tok0 + i < p.m) {
+                                const float v = (uint32_t)(w[i] >> 32) == seq
+                                                    ? __uint_as_float((uint32_t)w[i])
+                                                    : wait_word(src + (size_t)i * p.n, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
+                                sum[i] = rr == 0 ? v : sum[i] + v;
+                            }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (tok0 + i < p.m) A.out[(size_t)(tok0 + i) * p.n + row] = sum[i];
                 }
             }
         } else if (p.mode == kModeLmHead) {
@@ -648,6 +665,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
         tmem_dealloc(tmem_base, kBsTmemCols);
     }
     if (p.world > 1 || p.mode == kModeLmHead) step_end(X, step_begin(X), gridDim.x);
+    host_done_signal(X, gridDim.x);
 }
 
 }  // namespace ws

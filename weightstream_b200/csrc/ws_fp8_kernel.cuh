@@ -637,6 +637,7 @@ __global__ void __launch_bounds__(fp8_threads(GT), 1) fp8_rowpar_kernel(const __
         // step_begin again: the value is unchanged until the last CTA publishes the next one below
         step_end(X, step_begin(X), gridDim.x);
     }
+    host_done_signal(X, gridDim.x);
 }
 
 }  // namespace ws

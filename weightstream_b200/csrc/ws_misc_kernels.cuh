@@ -5,6 +5,21 @@
 
 namespace ws {
 
+// Host-buffer calls with small inputs: the activations come out of the pinned host buffer (device-
+// readable under unified addressing) into device memory, 16 bytes per thread.  The step's main kernel
+// may become resident at once; it waits for this grid before it reads the activations.
+struct StageParams {
+    const uint4 *src;
+    uint4 *dst;
+    int64_t n16;
+};
+__global__ void __launch_bounds__(256) stage_in_kernel(const __grid_constant__ StageParams p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < p.n16) p.dst[i] = p.src[i];
+}
+
 struct CollRank {
     const float *in;
     float *out;

@@ -159,12 +159,15 @@ class Endpoint:
             raise WsError(st, "ws_tp_create failed")
         self.handle = h
         self._keep: list = []
+        self._host_args: dict = {}
+        self._host_call = self.lib.ws_fp8_rowpar_gemm_allreduce_host
 
     # -- life cycle
     def close(self) -> None:
         if getattr(self, "handle", None):
             self.lib.ws_tp_destroy(self.handle)
             self.handle = None
+            self._host_args.clear()
 
     def __del__(self):
         try:
@@ -282,16 +285,26 @@ class Endpoint:
         rows copied out inside the call, which returns only when they are valid."""
         m = x_host.shape[0]
         n, k = w.shape
-        a = Fp8GemmArgs()
-        a.x, a.ldx, a.x_dtype = None, k, x_dtype
-        a.m, a.n, a.k = m, n, k
-        a.w, a.ldw = w.data_ptr(), w.stride(0)
-        a.scales, a.scale_ld, a.scale_kind = scales.data_ptr(), scales.shape[1], _scale_kind(scales)
-        a.block_n, a.block_k = block
-        a.row0, a.k0 = row0, k0
+        # the argument struct of a (weight, shape) pair is built once: a decode loop calls this with
+        # the same weights every step, and filling a ctypes struct costs as much as the launch
+        key = (w.data_ptr(), scales.data_ptr(), m, n, k, w.stride(0), tuple(block), row0, k0, x_dtype)
+        hit = self._host_args.get(key)
+        if hit is None:
+            a = Fp8GemmArgs()
+            a.x, a.ldx, a.x_dtype = None, k, x_dtype
+            a.m, a.n, a.k = m, n, k
+            a.w, a.ldw = w.data_ptr(), w.stride(0)
+            a.scales, a.scale_ld, a.scale_kind = scales.data_ptr(), scales.shape[1], _scale_kind(scales)
+            a.block_n, a.block_k = block
+            a.row0, a.k0 = row0, k0
+            if len(self._host_args) >= 4096:
+                self._host_args.clear()
+            hit = self._host_args[key] = (a, C.byref(a), w, scales)  # the tensors stay alive with their entry
         out = np.empty((m, n), dtype=np.float32)
-        xh = np.ascontiguousarray(x_host)
-        self._ok(self.lib.ws_fp8_rowpar_gemm_allreduce_host(self.handle, C.byref(a), xh.ctypes.data, out.ctypes.data))
+        xh = x_host if x_host.flags["C_CONTIGUOUS"] else np.ascontiguousarray(x_host)
+        st = self._host_call(self.handle, hit[1], xh.ctypes.data, out.ctypes.data)
+        if st != WS_OK:
+            self._ok(st)
         return out
 
 
