@@ -300,7 +300,9 @@ def build_workload(wl: str, m: int, tp, synth, torch, dist, dev, sh, l2_bytes) -
         W.step, W.e2e, W.verify, W.ep = step, e2e, verify, ep
         W.abytes, W.h2d, W.d2h = algorithmic_bytes(m, N_OUT, kl), m * kl * 2, m * N_OUT * 4
         if wl == "o_proj" and world == 1 and m == 1:
-            W.captured_traffic = 58.85e6
+            W.captured_traffic = 58.86e6   # profiles/fp8_rowpar_kernel_o_proj_m1.md
+        if wl == "o_proj" and world == 1 and m == 64:
+            W.captured_traffic = 59.6e6    # profiles/fp8_bs_kernel_o_proj_m64.md
         return W
     if wl == "lm_head":
         vocab, k = VOCAB, K_HEAD
@@ -351,7 +353,7 @@ def build_workload(wl: str, m: int, tp, synth, torch, dist, dev, sh, l2_bytes) -
         W.abytes = vl * k + (-(-vl // BN) + 1) * (k // BK) * 4 + m * k * 2 + m * 4
         W.h2d, W.d2h = m * k * 2, m * 4
         if world == 1 and m == 1:
-            W.captured_traffic = 934.7e6
+            W.captured_traffic = 932.7e6   # profiles/fp8_bs_kernel_lm_head_m1.md
         return W
     if wl == "moe_down":
         E, n, k, top_k = MOE_E, N_OUT, MOE_K, MOE_TOPK

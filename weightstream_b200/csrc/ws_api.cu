@@ -70,6 +70,7 @@ struct ws_tp {
 namespace {
 
 constexpr int kSmemBudget = 227 * 1024 - 1024;  // opt-in maximum minus alignment slack
+constexpr int kHalfSmemBudget = 113 * 1024 - 1024;  // what lets two CTAs share an SM (228 KB, 1 KB reserved per CTA)
 
 ws_status_t fail(ws_tp *tp, ws_status_t code, const char *fmt, ...) {
     char buf[512];
@@ -418,6 +419,7 @@ struct BsPlan {
     int mp, tile_rows, ntiles, a_pitch, b_pitch, slabs_per_stage, nstages, nslot_max, nacc;
     int csize;  // 2: CTA pairs share a tile, each CTA streams half of K (tiles of a lone CTA would fill under half of the MMA's rows)
     int ncta;   // CTAs the plan is for (even with pairs)
+    int tmem_cols;  // tensor-memory columns the CTA allocates (a power of two)
     size_t smem;
 };
 static BsPlan bs_plan(const ws_fp8_gemm_args_t &a, int mt, int skb, int ncta, bool pairs_allowed) {
@@ -443,20 +445,35 @@ static BsPlan bs_plan(const ws_fp8_gemm_args_t &a, int mt, int skb, int ncta, bo
     // slabs per stage: one MMA commit (a ~160 ns stall of the issuing thread) per stage, so several
     // slabs share it; bounded by the stage size and by tensor memory (each slab has its own
     // accumulator buffer: groups x slabs x (mp + 4) + 8 columns of 512, at least two groups)
-    u.slabs_per_stage = std::max(1, std::min({4, (56 * 1024) / slab_bytes, 504 / (2 * (u.mp + 4)), kslabs}));
     u.nslot_max = (tiles_per_cta * u.tile_rows) / a.block_n + 2;
-    u.nacc = std::min((int)kBsMaxAcc, 504 / (u.slabs_per_stage * (u.mp + 4)));
     const int rx_rows = u.csize == 2 ? mt : 0;
-    const int fixed = bs_smem_layout(0, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp, rx_rows).total;
-    int ns = (kSmemBudget - fixed - 1024 - kBsMmaRows * 128) / (u.slabs_per_stage * slab_bytes);
-    const int items = tiles_per_cta * ((kslabs / u.csize + u.slabs_per_stage - 1) / u.slabs_per_stage);
-    ns = std::min(ns, std::min((int)kMaxStages, std::max(2, items)));
-    u.nstages = ns;
-    // the epilogue and the producer wait on the same per-stage barrier: the MMA thread must not get a
-    // whole lap of the stage ring ahead of the epilogue, which holds when groups <= stages
-    u.nacc = std::max(1, std::min(u.nacc, ns));
-    u.ok = ns >= 2;
-    if (u.ok) u.smem = (size_t)bs_smem_layout(ns, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp, rx_rows).total + 1024;
+    // Half an SM (shared memory and tensor memory) when the tokens are few and the CTA's whole share of
+    // the weights fits such a ring (TP-8 shards): the next step's CTA is then resident beside this one
+    // (one CTA per SM and step) and loads all of its weights under this step's exchange and exit.
+    // Measured on B200, K/rank 1024, 8 rows: 7.7 us per step against 10.6.  Larger shares lose more to
+    // the shallower ring than they gain (K/rank 8192: 19.3 against 17.8 us).
+    const bool small = u.mp == 16 && (int64_t)a.n * a.k / u.ncta * u.csize <= ((int64_t)2 << 20);
+    for (int half = small ? 1 : 0; half >= 0; --half) {
+        const int budget = half ? kHalfSmemBudget : kSmemBudget, tmem = half ? 256 : 512;
+        const int stage_target = half ? 32 * 1024 : 56 * 1024;
+        u.slabs_per_stage = std::max(1, std::min({4, stage_target / slab_bytes, (tmem - 8) / (2 * (u.mp + 4)), kslabs}));
+        u.nacc = std::min((int)kBsMaxAcc, (tmem - 8) / (u.slabs_per_stage * (u.mp + 4)));
+        int ns = kMaxStages;  // the most stages whose layout fits
+        while (ns >= 2 && bs_smem_layout(ns, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp, rx_rows).total + 1024 > budget) --ns;
+        const int items = tiles_per_cta * ((kslabs / u.csize + u.slabs_per_stage - 1) / u.slabs_per_stage);
+        ns = std::min(ns, std::min((int)kMaxStages, std::max(2, items)));
+        u.nstages = ns;
+        // the epilogue and the producer wait on the same per-stage barrier: the MMA thread must not get a
+        // whole lap of the stage ring ahead of the epilogue, which holds when groups <= stages
+        u.nacc = std::max(1, std::min(u.nacc, ns));
+        u.ok = ns >= 2;
+        if (!u.ok || (half && items > ns)) continue;  // half an SM only when the CTA's whole share of the weights fits the ring
+        u.smem = (size_t)bs_smem_layout(ns, u.slabs_per_stage, u.a_pitch, u.b_pitch, u.nslot_max, skb, u.mp, rx_rows).total + 1024;
+        int cols = 32;
+        while (cols < u.nacc * u.slabs_per_stage * (u.mp + 4) + 4) cols *= 2;
+        u.tmem_cols = half ? std::min(cols, 256) : 512;
+        break;
+    }
     return u;
 }
 
@@ -489,6 +506,7 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
     p.tile_rows = u.tile_rows; p.ntiles = u.ntiles; p.a_pitch = u.a_pitch; p.b_pitch = u.b_pitch;
     p.slabs_per_stage = u.slabs_per_stage; p.nstages = u.nstages; p.nslot_max = u.nslot_max; p.skb = skb; p.nacc = u.nacc;
     p.csize = u.csize;
+    p.tmem_cols = u.tmem_cols;
     ncta = u.ncta;
     p.timeout_ns = t0->timeout_ns;
     p.lay = t0->lay;
@@ -530,7 +548,7 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
         cudaStream_t cs = static_cast<cudaStream_t>(streams ? streams[0] : nullptr);
         ws_status_t s = launch(t0, act_prep_kernel, q, prep_blocks, n, 256, 0, cs, t0->pdl != 0, false);
         if (s != WS_OK) return s;
-        return launch(t0, kernel, p, ncta, n, kBsThreads, u.smem, cs, t0->pdl != 0, true, u.csize);
+        return launch(t0, kernel, p, ncta, n, bs_threads(u.mp), u.smem, cs, t0->pdl != 0, true, u.csize);
     }
     for (int i = 0; i < n; ++i) {
         BsParams pi = p;
@@ -543,7 +561,7 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
         WS_CUDA(ranks[i], cudaSetDevice(ranks[i]->device));
         cudaStream_t cs = static_cast<cudaStream_t>(streams ? streams[i] : nullptr);
         ws_status_t s = launch(ranks[i], act_prep_kernel, qi, prep_blocks, 1, 256, 0, cs, t0->pdl != 0, false);
-        if (s == WS_OK) s = launch(ranks[i], kernel, pi, ncta, 1, kBsThreads, u.smem, cs, t0->pdl != 0, true, u.csize);
+        if (s == WS_OK) s = launch(ranks[i], kernel, pi, ncta, 1, bs_threads(u.mp), u.smem, cs, t0->pdl != 0, true, u.csize);
         if (s != WS_OK) { t0->err = ranks[i]->err; return s; }
     }
     return WS_OK;
@@ -555,21 +573,22 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
 // 208 us on CUDA cores; 58.7 MB 17.7 against 17.2 us, 14.7 MB 8.8 against 6.8 us, 7.3 MB 12.8 against 5.9 us).
 // A step that also gathers the logits stays on the CUDA-core kernel: the tensor-memory kernel leaves
 // only the argmax candidates (the decode loop's form of the call).
-static bool bs_wanted(const ws_tp *t0, int mt, const ws_fp8_gemm_args_t &a, bool gathers_logits) {
+static bool bs_wanted(const ws_tp *t0, int mt, const ws_fp8_gemm_args_t &a, bool gathers_logits, bool lm_head = false) {
     if (gathers_logits) return false;
     if (t0->kernel_sel == 2) return true;
     if (t0->kernel_sel != 0) return false;
-    return mt >= 3 || (int64_t)a.n * a.k >= ((int64_t)128 << 20);
+    // an argmax-only lm_head step also saves the exchange of one candidate per CTA (this kernel sends one per rank)
+    return mt >= 3 || (int64_t)a.n * a.k >= ((int64_t)(lm_head ? 32 : 128) << 20);
 }
 
 // Activation rows the next launch takes: up to 64 when their quantised copies fit in shared
 // memory beside at least three weight stages (the weights are then streamed once for all of
 // them), else 8.
-static int fp8_rows_per_launch(const ws_tp *t0, const ws_fp8_gemm_args_t &a, int ncta, int rem, bool gathers_logits) {
+static int fp8_rows_per_launch(const ws_tp *t0, const ws_fp8_gemm_args_t &a, int ncta, int rem, bool gathers_logits, bool lm_head = false) {
     {   // the tensor-memory path streams the weights once for up to 64 rows
         const int mt = std::min(rem, (int)kBsMaxTokens);
         const int skb = (int)((a.k0 + a.k - 1) / a.block_k - a.k0 / a.block_k + 1);
-        if (bs_wanted(t0, mt, a, gathers_logits) && bs_plan(a, mt, skb, ncta, false).ok) return mt;
+        if (bs_wanted(t0, mt, a, gathers_logits, lm_head) && bs_plan(a, mt, skb, ncta, false).ok) return mt;
     }
     if (rem <= 8) return rem;
     const int kbox = (a.k + 127) / 128;
@@ -590,7 +609,7 @@ static ws_status_t fp8_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t
     const ws_fp8_gemm_args_t &a0 = lm ? lm[0].g : args[0];
     bool gathers_logits = false;
     for (int i = 0; lm && i < n; ++i) gathers_logits |= lm[i].logits != nullptr;
-    if (bs_wanted(t0, mt, a0, gathers_logits)) {  // tensor-memory path whenever the shape fits it
+    if (bs_wanted(t0, mt, a0, gathers_logits, lm != nullptr)) {  // tensor-memory path whenever the shape fits it
         int64_t skb_u = 1;
         for (int i = 0; i < n; ++i) {
             const ws_fp8_gemm_args_t &a = lm ? lm[i].g : args[i];
@@ -740,7 +759,7 @@ ws_status_t ws_lm_head_allgather_argmax_group(ws_tp_t *const *ranks, int32_t n, 
     if (any_logits && args[0].vocab > t0->cfg.max_vocab)
         return fail(t0, WS_ERR_CAPACITY, "vocab=%d exceeds the endpoint's max_vocab=%d", args[0].vocab, t0->cfg.max_vocab);
     for (int m0 = 0; m0 < args[0].g.m;) {
-        const int mt = fp8_rows_per_launch(t0, args[0].g, ncta, args[0].g.m - m0, any_logits);
+        const int mt = fp8_rows_per_launch(t0, args[0].g, ncta, args[0].g.m - m0, any_logits, true);
         s = fp8_step(ranks, n, nullptr, args, m0, mt, streams, ncta, same, m0 + mt >= args[0].g.m);
         if (s != WS_OK) return s;
         m0 += mt;

@@ -41,8 +41,13 @@
 
 namespace ws {
 
-constexpr int kBsThreads = 192;      // warp 0: producer, warp 1: MMA issue (and owner of the tensor memory), warps 2-5: epilogue
-constexpr int kBsTmemCols = 512;
+// Threads of a CTA.  Warp 0: producer, warp 1: MMA issue (and owner of the tensor memory), then the
+// epilogue warps: four (one per 32-lane quarter of the tensor memory, all token columns) for up to 32
+// tokens, eight (two per quarter, half of the token columns each) for 64, where reading the
+// accumulators back is what a stage waits for (measured on B200, 64 rows: lm_head 324 -> 249 us;
+// with 32 rows eight warps were 3 % slower than four).
+__host__ __device__ constexpr int bs_epi_warps(int mp) { return mp >= 64 ? 8 : 4; }
+__host__ __device__ constexpr int bs_threads(int mp) { return 64 + 32 * bs_epi_warps(mp); }
 constexpr int kBsMaxAcc = 8;         // accumulator groups in tensor memory (a group = one stage's slabs)
 constexpr int kBsMaxTokens = 64;     // activation rows one launch takes
 constexpr int kBsAtomBytes = 512;    // one scale atom: 128 rows x 4 K blocks
@@ -93,7 +98,7 @@ struct alignas(64) BsParams {
     CUtensorMap tmap_w[WS_MAX_WORLD];  // weight shard [n][k bytes], box 128 bytes x tile_rows, 128B swizzle
     CUtensorMap tmap_x[WS_MAX_WORLD];  // quantised activations [mp][k bytes], box 128 bytes x mp, 128B swizzle
     int32_t m, mp, n, k, bn_shift, bk_shift;
-    int32_t world, mode, vocab, pad1;
+    int32_t world, mode, vocab, tmem_cols;  // tmem_cols: tensor-memory columns to allocate (512, or at most 256 when two CTAs share an SM)
     int32_t pad0;
     int32_t csize;                     // 1, or 2: CTA pairs (a cluster) share a tile, each streams half of K
     int32_t tile_rows, ntiles;         // output rows per tile (<= 128) and tiles of the shard
@@ -122,7 +127,7 @@ __host__ __device__ inline BsSmem bs_smem_layout(int nstages, int slabs_per_stag
     s.sf = o;   o += nsl * kBsAtomBytes;
     s.sfa = o;  o += kBsAtomBytes;
     s.sw = o;   o += (int)align_up((int64_t)nslot_max * skb * 4, 16);
-    s.cand = o; o += 4 * mp * 8;                         // lm_head: per epilogue warp and token (value, index)
+    s.cand = o; o += bs_epi_warps(mp) * mp * 8;          // lm_head: per epilogue warp and token (value, index)
     s.rx = o;   o += rx_rows * kBsMmaRows * 4;           // CTA pairs: the partner's partial sums of one tile, [token][row]
     s.bars = o; o += (2 * kMaxStages + kBsMaxAcc + 2) * 8;
     s.misc = o; o += 64;
@@ -250,7 +255,10 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     return false;
 }
 
-__device__ __forceinline__ void bs_epi_bar() { asm volatile("bar.sync 2, 128;" ::: "memory"); }  // warps 2-5
+template <int THREADS>
+__device__ __forceinline__ void bs_epi_bar_n() {  // the epilogue warps
+    asm volatile("bar.sync 2, %0;" ::"n"(THREADS) : "memory");
+}
 
 // The sequence of stage items of one CTA.  The shard's rows are cut into tiles of tile_rows rows
 // (at most 128, the M of the MMA; chosen so that the tiles deal out evenly) and CTA c takes tiles
@@ -282,7 +290,10 @@ struct BsWalk {
 };
 
 template <int MP>
-__global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_constant__ BsParams p) {
+__global__ void __launch_bounds__(bs_threads(MP), 1) fp8_bs_kernel(const __grid_constant__ BsParams p) {
+    constexpr int EW = bs_epi_warps(MP), ET = EW * 32;  // epilogue warps / threads
+    constexpr int CP = MP * 4 / EW;                      // token columns one epilogue thread holds
+    auto bs_epi_bar = [] { bs_epi_bar_n<ET>(); };
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     uint8_t *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -319,16 +330,16 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
             mbar_init(full0 + s * 8, 1);
             mbar_init(done0 + s * 8, 1);
         }
-        for (int b = 0; b < kBsMaxAcc; ++b) mbar_init(accempty0 + b * 8, 4);  // one arrival per epilogue warp
-        mbar_init(rxfull, 128);   // every epilogue thread of the partner arrives after its stores
-        mbar_init(rxempty, 128);
+        for (int b = 0; b < kBsMaxAcc; ++b) mbar_init(accempty0 + b * 8, EW);  // one arrival per epilogue warp
+        mbar_init(rxfull, ET);   // every epilogue thread of the partner arrives after its stores
+        mbar_init(rxempty, ET);
         mbar_fence_init();
     }
     if (warp == 1) {  // tensor memory: allocated and freed by the same warp
-        tmem_alloc(smem_u32(misc_s), kBsTmemCols);
+        tmem_alloc(smem_u32(misc_s), (uint32_t)p.tmem_cols);
         tmem_relinquish();
     }
-    if (warp >= 2) {  // the weight operand's scale atom: 2^0 everywhere (128 threads x 4 bytes)
+    if (warp >= 2 && warp < 6) {  // the weight operand's scale atom: 2^0 everywhere (128 threads x 4 bytes)
         uint32_t *sfa = reinterpret_cast<uint32_t *>(smem + S.sfa);
         sfa[tid - 64] = 0x7F7F7F7Fu;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -424,10 +435,12 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------ epilogue warps 2-5
-        const int et = tid - 64;                     // 0..127
-        const int quad = warp & 3;                   // TMEM lanes this warp may read
+        // ------------------------------------------------------------ epilogue warps
+        const int et = tid - 64;                     // 0..ET-1
+        const int ew = warp - 2;                     // 0..EW-1
+        const int quad = warp & 3;                   // TMEM lanes this warp may read: its index modulo 4
         const int rc = quad * 32 + lane;             // row inside the tile = TMEM lane
+        const int col0 = (ew >> 2) * CP;             // first token column of this thread
         const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
         const int t_lo = (int)((int64_t)ntiles * part / nparts), t_hi = (int)((int64_t)ntiles * (part + 1) / nparts) - 1;  // this CTA's tiles
         // weight scales of the rows this CTA touches as fp32: sw_s[slot][column].  They are static, so
@@ -437,7 +450,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
         const int64_t srow_lo = (A.row0 + row_lo) >> p.bn_shift;
         const int nslot = row_hi > row_lo ? (int)(((A.row0 + row_hi - 1) >> p.bn_shift) - srow_lo + 1) : 0;
         const int ncols = (int)(((A.k0 + p.k - 1) >> p.bk_shift) - kcol0 + 1);
-        for (int i = et; i < nslot * ncols; i += 128) {
+        for (int i = et; i < nslot * ncols; i += ET) {
             const int sl = i / ncols, c = i - sl * ncols;
             sw_s[sl * p.skb + c] = __ldg(static_cast<const float *>(A.scales) + (srow_lo + sl) * A.scale_ld + kcol0 + c);
         }
@@ -449,26 +462,26 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
         const bool solo = p.mode == kModeAllReduce && p.world == 1;
         const size_t astride = (size_t)p.lay.max_m * p.lay.max_n;
         const int nflag = kMaxCtas + kMaxShared;
-        float *cv_s = reinterpret_cast<float *>(smem + S.cand);        // [4 warps][MP]
-        uint32_t *ci_s = reinterpret_cast<uint32_t *>(smem + S.cand) + 4 * MP;
+        float *cv_s = reinterpret_cast<float *>(smem + S.cand);        // [EW warps][MP]; a warp fills its own columns
+        uint32_t *ci_s = reinterpret_cast<uint32_t *>(smem + S.cand) + EW * MP;
         if (p.mode == kModeLmHead)
-            for (int i = lane; i < MP; i += 32) { cv_s[(warp - 2) * MP + i] = -INFINITY; ci_s[(warp - 2) * MP + i] = 0xFFFFFFFFu; }
+            for (int i = lane; i < MP; i += 32) { cv_s[ew * MP + i] = -INFINITY; ci_s[ew * MP + i] = 0xFFFFFFFFu; }
 
         // A finished tile: its rows go to the output or to the peers; of an lm_head tile the candidates are kept.
-        auto finalize = [&](const float (&v)[MP], int tile) {
+        auto finalize = [&](const float (&v)[CP], int tile) {  // v[i]: token col0 + i
             const int row = tile * TR + rc;
             const bool mine = rc < TR && row < p.n;
             if (mine) {
                 if (solo) {
 #pragma unroll
-                    for (int t = 0; t < MP; ++t)
-                        if (t < p.m) A.out[(size_t)t * p.n + row] = v[t];
+                    for (int i = 0; i < CP; ++i)
+                        if (col0 + i < p.m) A.out[(size_t)(col0 + i) * p.n + row] = v[i];
                 } else if (p.mode == kModeAllReduce) {
                     for (int pr = 0; pr < p.world; ++pr) {
                         uint64_t *dst = reinterpret_cast<uint64_t *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
 #pragma unroll
-                        for (int t = 0; t < MP; ++t)
-                            if (t < p.m) st_word_sys(dst + (size_t)t * p.n + row, seq, v[t]);
+                        for (int i = 0; i < CP; ++i)
+                            if (col0 + i < p.m) st_word_sys(dst + (size_t)(col0 + i) * p.n + row, seq, v[i]);
                     }
                 }
             }
@@ -476,19 +489,20 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
                 // best (value, lowest index) of this warp's rows per token, merged into the warp's running best
                 const uint32_t idx = (uint32_t)(A.vocab_row0 + row);
 #pragma unroll
-                for (int t = 0; t < MP; ++t) {
+                for (int i = 0; i < CP; ++i) {
+                    const int t = col0 + i;
                     if (t >= p.m) break;
-                    float bv = (mine && v[t] > -INFINITY) ? v[t] : -INFINITY;
-                    uint32_t bi = (mine && v[t] > -INFINITY) ? idx : 0xFFFFFFFFu;
+                    float bv = (mine && v[i] > -INFINITY) ? v[i] : -INFINITY;
+                    uint32_t bi = (mine && v[i] > -INFINITY) ? idx : 0xFFFFFFFFu;
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) {
                         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
                         const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
                         if (cand_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
                     }
-                    if (lane == 0 && cand_better(bv, bi, cv_s[(warp - 2) * MP + t], ci_s[(warp - 2) * MP + t])) {
-                        cv_s[(warp - 2) * MP + t] = bv;
-                        ci_s[(warp - 2) * MP + t] = bi;
+                    if (lane == 0 && cand_better(bv, bi, cv_s[ew * MP + t], ci_s[ew * MP + t])) {
+                        cv_s[ew * MP + t] = bv;
+                        ci_s[ew * MP + t] = bi;
                     }
                 }
             }
@@ -498,12 +512,12 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
         RingPos st, ag;  // stage ring, accumulator-group ring
         bool ok = true;
         int tile, s0, nsl, ntile_done = 0;
-        float acc[MP];
+        float acc[CP];
         const float *swrow = sw_s;
         while (w.next(tile, s0, nsl)) {
             if (s0 == k_lo) {  // a new tile
 #pragma unroll
-                for (int i = 0; i < MP; ++i) acc[i] = 0.0f;
+                for (int i = 0; i < CP; ++i) acc[i] = 0.0f;
                 const int row = min(tile * TR + min(rc, TR - 1), p.n - 1);
                 swrow = sw_s + (int)(((A.row0 + row) >> p.bn_shift) - srow_lo) * p.skb;
             }
@@ -514,10 +528,10 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
             if (ok) {
                 for (int j = 0; j < nsl; ++j) {
                     const float sw = swrow[(kofs + (s0 + j) * 128) >> p.bk_shift];
-                    uint32_t r[MP];
-                    tmem_ld_cols<MP>(tlane + (uint32_t)((g * SL + j) * MP), r);  // returns once the values are in registers
+                    uint32_t r[CP];
+                    tmem_ld_cols<CP>(tlane + (uint32_t)((g * SL + j) * MP + col0), r);  // returns once the values are in registers
 #pragma unroll
-                    for (int i = 0; i < MP; ++i) acc[i] = fmaf(__uint_as_float(r[i]), sw, acc[i]);
+                    for (int i = 0; i < CP; ++i) acc[i] = fmaf(__uint_as_float(r[i]), sw, acc[i]);
                 }
             }
             tc_fence_before();
@@ -533,16 +547,16 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
                     if (ntile_done > 0) mbar_wait_cluster(rxempty, (uint32_t)(ntile_done - 1) & 1u, X.status);  // the previous tile's have been read
                     const uint32_t dst = mapa_u32(smem_u32(smem + S.rx) + (uint32_t)rc * 4u, 0u);
 #pragma unroll
-                    for (int t = 0; t < MP; ++t)
-                        if (t < p.m) st_cluster_f32(dst + (uint32_t)(t * kBsMmaRows * 4), acc[t]);
+                    for (int i = 0; i < CP; ++i)
+                        if (col0 + i < p.m) st_cluster_f32(dst + (uint32_t)((col0 + i) * kBsMmaRows * 4), acc[i]);
                     mbar_arrive_cluster(mapa_u32(rxfull, 0u));
                 } else {
                     // first CTA: K half 0 (own) + K half 1 (the partner's), in that order
                     mbar_wait_cluster(rxfull, (uint32_t)ntile_done & 1u, X.status);
                     const float *rx = reinterpret_cast<const float *>(smem + S.rx) + rc;
 #pragma unroll
-                    for (int t = 0; t < MP; ++t)
-                        if (t < p.m) acc[t] += rx[t * kBsMmaRows];
+                    for (int i = 0; i < CP; ++i)
+                        if (col0 + i < p.m) acc[i] += rx[(col0 + i) * kBsMmaRows];
                     mbar_arrive_cluster(mapa_u32(rxempty, 1u));
                     finalize(acc, tile);
                 }
@@ -550,7 +564,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
             }
         }
 
-        // ---- exchange (the 128 epilogue threads)
+        // ---- exchange (the epilogue threads)
         const uint32_t *myflags = solo ? nullptr
                                        : reinterpret_cast<const uint32_t *>(X.sym[X.rank] + p.lay.flags_off) + (size_t)bank * p.world * nflag;
         if (!solo && p.mode == kModeAllReduce) {
@@ -562,17 +576,18 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
                 // 16 tokens at a time: their words of one rank are all requested before the first is
                 // looked at (one memory round trip per batch, not per word); a word that has not
                 // arrived yet is then waited for on its own.  Ranks are added in rank order.
-                for (int tok0 = 0; tok0 < p.m; tok0 += 16) {
+                const int tend = min(p.m, col0 + CP);  // this thread's token columns
+                for (int tok0 = col0; tok0 < tend; tok0 += 16) {
                     float sum[16];
                     for (int rr = 0; rr < p.world; ++rr) {
                         const uint64_t *src = slots + rr * astride + (size_t)tok0 * p.n + row;
                         uint64_t w[16];
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            if (tok0 + i < p.m) w[i] = ld_word_sys(src + (size_t)i * p.n);
+                            if (tok0 + i < tend) w[i] = ld_word_sys(src + (size_t)i * p.n);
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            if (tok0 + i < p.m) {
+                            if (tok0 + i < tend) {
                                 const float v = (uint32_t)(w[i] >> 32) == seq
                                                     ? __uint_as_float((uint32_t)w[i])
                                                     : wait_word(src + (size_t)i * p.n, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
@@ -581,7 +596,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
                     }
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
-                        if (tok0 + i < p.m) A.out[(size_t)(tok0 + i) * p.n + row] = sum[i];
+                        if (tok0 + i < tend) A.out[(size_t)(tok0 + i) * p.n + row] = sum[i];
                 }
             }
         } else if (p.mode == kModeLmHead) {
@@ -591,10 +606,11 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
             // per peer and step instead of one per CTA.
             bs_epi_bar();
             uint64_t *table = reinterpret_cast<uint64_t *>(X.sym[X.rank] + p.lay.pairs_off) + (size_t)bank * p.world * kMaxCtas * p.lay.max_m;
-            if (et < p.m) {
-                float bv = cv_s[et];
-                uint32_t bi = ci_s[et];
-                for (int w = 1; w < 4; ++w)
+            if (et < p.m) {  // token et: the four warps (one per lane quarter) that hold its column
+                const int w0 = (et / CP) * 4;
+                float bv = cv_s[w0 * MP + et];
+                uint32_t bi = ci_s[w0 * MP + et];
+                for (int w = w0 + 1; w < w0 + 4; ++w)
                     if (cand_better(cv_s[w * MP + et], ci_s[w * MP + et], bv, bi)) { bv = cv_s[w * MP + et]; bi = ci_s[w * MP + et]; }
                 table[((size_t)X.rank * kMaxCtas + cta) * p.lay.max_m + et] = ((uint64_t)__float_as_uint(bv) << 32) | bi;
             }
@@ -629,7 +645,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
                     }
                     return ((uint64_t)__float_as_uint(bv) << 32) | bi;
                 };
-                for (int t = warp - 2; t < p.m; t += 4) {
+                for (int t = ew; t < p.m; t += EW) {
                     const uint64_t best = merge(t, ncta, [&](int i) { return table + ((size_t)X.rank * kMaxCtas + i) * p.lay.max_m; });
                     if (lane < p.world) {
                         uint64_t *dst = reinterpret_cast<uint64_t *>(X.sym[lane] + p.lay.pairs_off) +
@@ -645,7 +661,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
                 }
                 bs_epi_bar();
                 if (A.argmax != nullptr)
-                    for (int t = warp - 2; t < p.m; t += 4) {
+                    for (int t = ew; t < p.m; t += EW) {
                         const uint64_t best = merge(t, p.world, [&](int i) { return table + ((size_t)i * kMaxCtas + kRankRow) * p.lay.max_m; });
                         if (lane == 0) A.argmax[t] = ((uint32_t)best == 0xFFFFFFFFu) ? 0u : (uint32_t)best;
                     }
@@ -662,7 +678,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) fp8_bs_kernel(const __grid_cons
     }
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, kBsTmemCols);
+        tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
     }
     if (p.world > 1 || p.mode == kModeLmHead) step_end(X, step_begin(X), gridDim.x);
     host_done_signal(X, gridDim.x);
