@@ -185,12 +185,13 @@ ws_status_t ws_act_quant_fp8(const void *x, int64_t ldx, int32_t x_dtype, int32_
  * that do not fill whole 16-row tiles on every CTA out row by row, so that every SM streams
  * the same number of bytes; 0 hands each leftover tile to one CTA whole. */
 ws_status_t ws_tp_set_split(ws_tp_t *tp, int32_t on);
-/* Kernel choice, also without counterpart in the reference.  0 (default) automatic: FP8 steps
- * run one or two activation rows on CUDA cores and three or more through the tensor-core MMA,
- * the MoE step runs its decode form (prep kernel + CUDA-core kernel).  1: the mma.sync
- * formulation for every FP8 row count and the MMA form of the MoE step.  2: the tcgen05 /
- * tensor-memory FP8 kernel whenever the shape fits it.  All choices give results within the same
- * tolerance of the reference arithmetic; ranks of one group must make the same choice. */
+/* Kernel choice, also without counterpart in the reference.  0 (default) automatic: FP8 steps run
+ * one or two activation rows on CUDA cores and three or more (and shards from 128 MB) on the
+ * block-scaled tcgen05 kernel; the MoE step runs on its tcgen05 kernel when the shape fits it
+ * (k <= 4096, one rank per launch), else on its CUDA-core decode form.  1: the mma.sync
+ * formulations.  2: the tcgen05 kernels wherever the shape fits.  3: the CUDA-core kernels (MoE: the
+ * decode form).  All choices give results within the same tolerance of the reference arithmetic;
+ * ranks of one group must make the same choice. */
 ws_status_t ws_tp_set_kernel(ws_tp_t *tp, int32_t which);
 
 /* ---- FP8 GEMM for callers that must not allocate ------------------------------------------

@@ -19,6 +19,7 @@
 #include "ws_misc_kernels.cuh"
 #include "ws_moe_kernel.cuh"
 #include "ws_moe_gemv_kernel.cuh"
+#include "ws_moe_bs_kernel.cuh"
 
 using namespace ws;
 
@@ -62,6 +63,7 @@ struct ws_tp {
     float *moe_acc = nullptr;
     size_t moe_acc_bytes = 0;
     // block-scaled tcgen05 step: the step's quantised activations [64][k] and their scale atoms
+    int moe_bs = 1;  // 0: the MoE step stays on the CUDA-core decode form
     uint8_t *bs_work = nullptr;
     size_t bs_work_bytes = 0;
     std::string err;
@@ -122,6 +124,26 @@ ws_status_t make_tmap(ws_tp *tp, CUtensorMap *map, const void *base, uint64_t ro
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(tp, WS_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return WS_OK;
+}
+
+// Expert slab [experts][rows][k] of packed 4-bit codes (row stride k/2 bytes), boxes of 128 codes x
+// box_rows x 1 expert; the copy unpacks 16 codes (8 bytes) into 16 bytes of shared memory, the form
+// tcgen05.mma.kind::mxf8f6f4 reads 4-bit operands in; 128B swizzle.
+ws_status_t make_tmap_fp4(ws_tp *tp, CUtensorMap *map, const void *base, uint64_t experts, uint64_t rows, uint64_t k,
+                          uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(tp, WS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    if ((reinterpret_cast<uintptr_t>(base) & 31) || (k & 255))
+        return fail(tp, WS_ERR_INVALID, "expert slab must be 32-byte aligned with k a multiple of 256");
+    cuuint64_t dims[3] = {k, rows, experts};
+    cuuint64_t strides[2] = {k / 2, rows * (k / 2)};
+    cuuint32_t box[3] = {128, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(tp, WS_ERR_CUDA, "cuTensorMapEncodeTiled (4-bit) failed (%d)", (int)r);
     return WS_OK;
 }
 
@@ -276,7 +298,8 @@ ws_status_t ws_tp_create(int32_t world, int32_t rank, int32_t device, const ws_t
     if (set_smem(tp, moe_gemv_kernel) != WS_OK || set_smem(tp, fp8_rowpar_kernel<0>) != WS_OK || set_smem(tp, fp8_rowpar_kernel<1>) != WS_OK ||
         set_smem(tp, fp8_rowpar_kernel<2>) != WS_OK || set_smem(tp, moe_down_kernel) != WS_OK ||
         set_smem(tp, fp8_bs_kernel<16>) != WS_OK || set_smem(tp, fp8_bs_kernel<32>) != WS_OK ||
-        set_smem(tp, fp8_bs_kernel<64>) != WS_OK ||
+        set_smem(tp, fp8_bs_kernel<64>) != WS_OK || set_smem(tp, moe_bs_kernel) != WS_OK ||
+        cudaFuncSetAttribute(moe_bs_prep_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
         // The prep kernel uses no shared memory, but a main-kernel CTA (which needs almost all of an SM's)
         // cannot move onto an SM whose L1/shared split must first change, and that has to wait for the prep
         // blocks there to leave: measured 2.5-4.5 us of late CTAs.  With the same preference nothing changes.
@@ -786,11 +809,79 @@ static ws_status_t ensure_moe_scratch(ws_tp *tp, size_t work_bytes, size_t acc_b
     }
     if (acc_bytes > tp->moe_acc_bytes) {
         if (tp->moe_acc) cudaFree(tp->moe_acc);
-    if (tp->bs_work) cudaFree(tp->bs_work);
         tp->moe_acc = nullptr;
         tp->moe_acc_bytes = 0;
         WS_CUDA(tp, cudaMalloc(&tp->moe_acc, acc_bytes));
         tp->moe_acc_bytes = acc_bytes;
+    }
+    return WS_OK;
+}
+
+// Plan of the MoE step on the tcgen05 path; ok = false when the shape does not fit it (CTA pairs split K
+// in halves of at most 16 slabs, a pair's rows are one MMA tile, the per-token sums live in shared memory).
+struct MoeBsPlan {
+    bool ok;
+    int ncta, tile_rows, a_pitch, slabs_per_stage, nstages, tmem_cols;
+    size_t smem;
+};
+static MoeBsPlan moe_bs_plan(const ws_moe_down_args_t &a, int ncta) {
+    MoeBsPlan u{};
+    u.ncta = ncta & ~1;
+    const int nparts = u.ncta / 2, kslabs = a.k / 128;
+    if (nparts < 1 || a.k % 256 || kslabs / 2 > kMoeBsMaxSlabs || a.m > kBsMaxTokens) return u;
+    u.tile_rows = (a.n + nparts - 1) / nparts;
+    if (u.tile_rows > kBsMmaRows) return u;
+    u.a_pitch = (u.tile_rows + 7) / 8 * 8 * 128;
+    const int nslab = kslabs / 2, slab_bytes = u.a_pitch + kMoeBsCols * 128 + kBsAtomBytes;
+    u.slabs_per_stage = std::max(1, std::min({4, (32 * 1024) / slab_bytes, nslab}));
+    int ns = kMaxStages;
+    while (ns >= 2 && moe_bs_smem_layout(ns, u.slabs_per_stage, u.a_pitch, a.m, nslab).total + 1024 > kSmemBudget) --ns;
+    u.nstages = ns;
+    int cols = 32;
+    while (cols < 2 * kMoeBsCols + 2 * nslab * 8) cols *= 2;
+    u.tmem_cols = cols;
+    u.ok = ns >= 2 && cols <= 512;
+    if (u.ok) u.smem = (size_t)moe_bs_smem_layout(ns, u.slabs_per_stage, u.a_pitch, a.m, nslab).total + 1024;
+    return u;
+}
+
+// The MoE step on the block-scaled tcgen05 path: prep kernel, then the persistent CTA pairs.  One rank
+// per launch (a cluster launch cannot also be the cooperative launch virtual ranks need).
+static ws_status_t moe_bs_step(ws_tp *const *ranks, int n, const ws_moe_down_args_t *args, void *const *streams,
+                               const MoeBsPlan &u) {
+    ws_tp *t0 = ranks[0];
+    const ws_moe_down_args_t &a0 = args[0];
+    MoeBsParams p{};
+    p.m = a0.m; p.n = a0.n; p.k = a0.k; p.world = t0->world;
+    p.tile_rows = u.tile_rows; p.a_pitch = u.a_pitch; p.slabs_per_stage = u.slabs_per_stage; p.nstages = u.nstages;
+    p.tmem_cols = u.tmem_cols;
+    p.timeout_ns = t0->timeout_ns;
+    p.lay = t0->lay;
+    MoeBsPrepParams q{};
+    q.m = a0.m; q.k = a0.k; q.top_k = a0.top_k; q.h_dtype = a0.h_dtype;
+    const MoeBsWork W = moe_bs_work_layout(a0.k);
+    const int nblk = a0.m * a0.top_k + 1;
+    for (int i = 0; i < n; ++i) ranks[i]->step++;
+    for (int i = 0; i < n; ++i) {
+        ws_tp *t = ranks[i];
+        const ws_moe_down_args_t &a = args[i];
+        ws_status_t s = ensure_moe_scratch(t, (size_t)W.total, 0);
+        if (s == WS_OK) s = make_tmap_fp4(t, &p.tmap_w[0], a.w2, (uint64_t)a.e_len, (uint64_t)a.n, (uint64_t)a.k, (uint32_t)u.tile_rows);
+        if (s == WS_OK)
+            s = make_tmap(t, &p.tmap_x[0], t->moe_work + W.xq, (uint64_t)(kMoeMaxRoutes + kMoeBsCols), (uint64_t)a.k, (uint64_t)a.k,
+                          (uint32_t)kMoeBsCols);
+        if (s != WS_OK) { t0->err = t->err; return s; }
+        MoeBsRank &r = p.r[0];
+        r.s2 = a.s2; r.work = t->moe_work; r.out = a.out; r.e_start = a.e_start; r.e_len = a.e_len;
+        r.ctx = make_ctx(t);
+        MoePrepRank &pr = q.r[0];
+        pr.h = a.h; pr.route_ids = a.route_ids; pr.route_w = a.route_w; pr.work = t->moe_work;
+        pr.ldh = a.ldh; pr.e_start = a.e_start; pr.e_len = a.e_len;
+        WS_CUDA(t, cudaSetDevice(t->device));
+        cudaStream_t cs = static_cast<cudaStream_t>(streams ? streams[i] : nullptr);
+        s = launch(t, moe_bs_prep_kernel, q, nblk, 1, 256, 0, cs, t0->pdl != 0, false);
+        if (s == WS_OK) s = launch(t, moe_bs_kernel, p, u.ncta, 1, kMoeBsThreads, u.smem, cs, t0->pdl != 0, true, 2);
+        if (s != WS_OK) { t0->err = t->err; return s; }
     }
     return WS_OK;
 }
@@ -913,6 +1004,12 @@ ws_status_t ws_moe_down_combine_allreduce_group(ws_tp_t *const *ranks, int32_t n
     int e_len_all = args[0].e_len;
     for (int i = 0; i < n; ++i)
         if (args[i].e_len != e_len_all) return fail(t0, WS_ERR_INVALID, "ranks must hold equally many experts");
+    if (t0->kernel_sel != 1 && (n == 1 || !same) && (reinterpret_cast<uintptr_t>(a0.w2) & 31) == 0) {  // tcgen05 form
+        const MoeBsPlan u = moe_bs_plan(a0, ncta);
+        // measured on B200 (384 experts of 7168x2048, top-6): 64 tokens 676 us against 841 on CUDA cores;
+        // 1 and 8 tokens equal (23.6 and 130 us), so those stay on the kernel with the longer record
+        if (u.ok && t0->moe_bs && (t0->kernel_sel == 2 || a0.m * a0.top_k >= 96)) return moe_bs_step(ranks, n, args, streams, u);
+    }
     if (t0->kernel_sel != 1 && a0.k <= 32 * 32 * kMoeGemvWarps)  // decode form: CUDA-core matrix-vector products
         return moe_gemv_step(ranks, n, args, streams, ncta, same);
 
@@ -1248,10 +1345,12 @@ ws_status_t ws_act_quant_fp8(const void *x, int64_t ldx, int32_t x_dtype, int32_
     return cudaGetLastError() == cudaSuccess ? WS_OK : WS_ERR_CUDA;
 }
 
-// 0 (default): automatic; 1: the mma.sync kernel; 2: the block-scaled tcgen05 kernel when the shape fits.
+// 0 (default): automatic; 1: the mma.sync kernels; 2: the block-scaled tcgen05 kernels wherever the shape
+// fits; 3: the CUDA-core kernels (FP8: as automatic for one or two rows, mma.sync beyond; MoE: the decode form).
 ws_status_t ws_tp_set_kernel(ws_tp_t *tp, int32_t which) {
-    if (!tp || which < 0 || which > 2) return WS_ERR_INVALID;
+    if (!tp || which < 0 || which > 3) return WS_ERR_INVALID;
     tp->kernel_sel = which;
+    tp->moe_bs = which == 3 ? 0 : 1;
     return WS_OK;
 }
 

@@ -211,7 +211,8 @@ class Endpoint:
         self._ok(self.lib.ws_tp_set_split(self.handle, int(on)))
 
     def set_kernel(self, which: int) -> None:
-        """0: automatic (default); 1: the mma.sync kernel; 2: the tcgen05 kernel when the shape fits."""
+        """0: automatic (default); 1: the mma.sync kernels; 2: the tcgen05 kernels wherever the shape fits;
+        3: the CUDA-core kernels (MoE: the decode form)."""
         self._ok(self.lib.ws_tp_set_kernel(self.handle, int(which)))
 
     def check(self, stream=None) -> None:
