@@ -75,6 +75,19 @@ def main():
     want = O.allreduce_fold(np.stack([O.moe_down_combine(w2[a:a + el], s2[a:a + el], a, hf, ids, rw) for a in range(0, E, el)]))
     assert rel(y.cpu().numpy(), want) < 5e-5, "moe"
     assert same_everywhere(y, world), "moe ranks differ"
+    # the same step at the measured expert shape's K (2048) with 40 tokens: several passes per expert
+    kk2, mm = 2048, 40
+    w2b, s2b = synth.fp4_experts(rng, E, 512, kk2)
+    ids2, rw2 = synth.routes(rng, mm, E, top_k)
+    hb2 = F.f32_to_bf16_bits(rng.standard_normal((mm * top_k, kk2)).astype(np.float32))
+    y2 = ep.moe_down_combine_allreduce(torch.from_numpy(hb2.view(np.int16)).to(dev).view(torch.bfloat16),
+                                       torch.from_numpy(ids2).to(dev), torch.from_numpy(rw2).to(dev),
+                                       torch.from_numpy(w2b[e0:e0 + el]).to(dev), torch.from_numpy(s2b[e0:e0 + el]).to(dev), e0)
+    ep.check()
+    hf2 = F.bf16_bits_to_f32(hb2)
+    want2 = O.allreduce_fold(np.stack([O.moe_down_combine(w2b[a:a + el], s2b[a:a + el], a, hf2, ids2, rw2) for a in range(0, E, el)]))
+    assert rel(y2.cpu().numpy(), want2) < 5e-5, "moe, 40 tokens"
+    assert same_everywhere(y2, world), "moe (40 tokens) ranks differ"
     # lm_head, vocab sliced
     wv, sv = synth.fp8_weight(rng, vocab, 512)
     xv = synth.activations_bf16(rng, 2, 512)

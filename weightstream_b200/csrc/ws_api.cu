@@ -832,8 +832,10 @@ static MoeBsPlan moe_bs_plan(const ws_moe_down_args_t &a, int ncta) {
     u.tile_rows = (a.n + nparts - 1) / nparts;
     if (u.tile_rows > kBsMmaRows) return u;
     u.a_pitch = (u.tile_rows + 7) / 8 * 8 * 128;
-    const int nslab = kslabs / 2, slab_bytes = u.a_pitch + kMoeBsCols * 128 + kBsAtomBytes;
-    u.slabs_per_stage = std::max(1, std::min({4, (32 * 1024) / slab_bytes, nslab}));
+    const int nslab = kslabs / 2;
+    // a stage = 4 slabs (2 when the half of K is not a multiple of 4): one commit and one activation copy per stage
+    if (nslab % 2) return u;
+    u.slabs_per_stage = nslab % 4 ? 2 : 4;
     int ns = kMaxStages;
     while (ns >= 2 && moe_bs_smem_layout(ns, u.slabs_per_stage, u.a_pitch, a.m, nslab).total + 1024 > kSmemBudget) --ns;
     u.nstages = ns;
@@ -858,7 +860,7 @@ static ws_status_t moe_bs_step(ws_tp *const *ranks, int n, const ws_moe_down_arg
     p.timeout_ns = t0->timeout_ns;
     p.lay = t0->lay;
     MoeBsPrepParams q{};
-    q.m = a0.m; q.k = a0.k; q.top_k = a0.top_k; q.h_dtype = a0.h_dtype;
+    q.m = a0.m; q.k = a0.k; q.top_k = a0.top_k; q.h_dtype = a0.h_dtype; q.sl = u.slabs_per_stage;
     const MoeBsWork W = moe_bs_work_layout(a0.k);
     const int nblk = a0.m * a0.top_k + 1;
     for (int i = 0; i < n; ++i) ranks[i]->step++;
@@ -867,9 +869,6 @@ static ws_status_t moe_bs_step(ws_tp *const *ranks, int n, const ws_moe_down_arg
         const ws_moe_down_args_t &a = args[i];
         ws_status_t s = ensure_moe_scratch(t, (size_t)W.total, 0);
         if (s == WS_OK) s = make_tmap_fp4(t, &p.tmap_w[0], a.w2, (uint64_t)a.e_len, (uint64_t)a.n, (uint64_t)a.k, (uint32_t)u.tile_rows);
-        if (s == WS_OK)
-            s = make_tmap(t, &p.tmap_x[0], t->moe_work + W.xq, (uint64_t)(kMoeMaxRoutes + kMoeBsCols), (uint64_t)a.k, (uint64_t)a.k,
-                          (uint32_t)kMoeBsCols);
         if (s != WS_OK) { t0->err = t->err; return s; }
         MoeBsRank &r = p.r[0];
         r.s2 = a.s2; r.work = t->moe_work; r.out = a.out; r.e_start = a.e_start; r.e_len = a.e_len;
@@ -1006,9 +1005,9 @@ ws_status_t ws_moe_down_combine_allreduce_group(ws_tp_t *const *ranks, int32_t n
         if (args[i].e_len != e_len_all) return fail(t0, WS_ERR_INVALID, "ranks must hold equally many experts");
     if (t0->kernel_sel != 1 && (n == 1 || !same) && (reinterpret_cast<uintptr_t>(a0.w2) & 31) == 0) {  // tcgen05 form
         const MoeBsPlan u = moe_bs_plan(a0, ncta);
-        // measured on B200 (384 experts of 7168x2048, top-6): 64 tokens 676 us against 841 on CUDA cores;
-        // 1 and 8 tokens equal (23.6 and 130 us), so those stay on the kernel with the longer record
-        if (u.ok && t0->moe_bs && (t0->kernel_sel == 2 || a0.m * a0.top_k >= 96)) return moe_bs_step(ranks, n, args, streams, u);
+        // measured on B200 (384 experts of 7168x2048, top-6), tcgen05 against the CUDA-core decode form:
+        // 1 token 19.5 against 23.6 us, 8 tokens 95 against 130, 64 tokens 495 against 841
+        if (u.ok && t0->moe_bs) return moe_bs_step(ranks, n, args, streams, u);
     }
     if (t0->kernel_sel != 1 && a0.k <= 32 * 32 * kMoeGemvWarps)  // decode form: CUDA-core matrix-vector products
         return moe_gemv_step(ranks, n, args, streams, ncta, same);

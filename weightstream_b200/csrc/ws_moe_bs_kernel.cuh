@@ -44,23 +44,28 @@ constexpr int kMoeBsThreads = 320;    // warp 0 producer, 1 MMA issue, 2-5 epilo
 constexpr int kMoeBsMaxSlabs = 16;    // K slabs one CTA walks per pass (k <= 4096 with pairs)
 
 // Per-endpoint scratch written by moe_bs_prep_kernel and read by moe_bs_kernel.
+// The activations of a pass are stored as the main kernel's shared memory wants them, so that ONE bulk
+// copy fills a stage: per pass and group of `sl` K slabs, sl tiles of 16 rows x 128 bytes (128B-swizzled
+// K-major, the layout a TMA box would produce) followed by their sl scale atoms.
+constexpr int kMoeBsXTile = kMoeBsCols * 128;                 // 2048
+constexpr int kMoeBsXSlab = kMoeBsXTile + kBsAtomBytes;       // 2560 bytes of a stage per slab
 struct MoeBsWork {
-    int64_t hdr, pass, stok, xq, sfb, total;  // byte offsets
+    int64_t hdr, pass, stok, xs, total;  // byte offsets
 };
 __host__ __device__ inline MoeBsWork moe_bs_work_layout(int k) {
     MoeBsWork w{};
     int64_t o = 0;
     w.hdr = o;  o += 64;
     w.pass = o; o += (int64_t)kMoeMaxRoutes * sizeof(MoePass);
-    w.stok = o; o += align_up((int64_t)(kMoeMaxRoutes + kMoeBsCols) * 2, 64);
-    w.xq = o;   o += align_up((int64_t)(kMoeMaxRoutes + kMoeBsCols) * k, 256);   // a pass's box may run past its last route
-    w.sfb = o;  o += (int64_t)kMoeMaxRoutes * (k / 128) * kBsAtomBytes;            // one atom per pass and slab
+    w.stok = o; o += align_up((int64_t)(kMoeMaxRoutes + kMoeBsCols) * 2, 256);
+    w.xs = o;   o += (int64_t)kMoeMaxRoutes * (k / 128) * kMoeBsXSlab;  // [pass][slab group][tiles | atoms]
     w.total = o;
     return w;
 }
 
 struct MoeBsPrepParams {
     int32_t m, k, top_k, h_dtype;
+    int32_t sl, pad0;  // K slabs per stage of the main kernel (a group of the layout above)
     MoePrepRank r[WS_MAX_WORLD];
 };
 
@@ -128,8 +133,8 @@ __global__ void __launch_bounds__(256) moe_bs_prep_kernel(const __grid_constant_
         reinterpret_cast<uint16_t *>(A.work + W.stok)[pos] = (uint16_t)(route / p.top_k);
     }
     const float w = A.route_w[route];
-    uint8_t *xq = A.work + W.xq + (size_t)pos * p.k;
-    uint8_t *sfb = A.work + W.sfb + (size_t)pass * (p.k >> 7) * kBsAtomBytes + t * 16;
+    uint8_t *xs = A.work + W.xs + (size_t)pass * (p.k >> 7) * kMoeBsXSlab;
+    const int group_bytes = p.sl * kMoeBsXSlab;
     for (int c = tid; c < (p.k >> 3); c += blockDim.x) {  // the four chunks of a 32-block are adjacent lanes
         float v[8];
         load_act8(A.h, p.h_dtype, (int64_t)route * A.ldh + c * 8, true, v);
@@ -138,11 +143,13 @@ __global__ void __launch_bounds__(256) moe_bs_prep_kernel(const __grid_constant_
         int ex;
         uint32_t lo, hi;
         act_quant8(v, ex, lo, hi);
-        *reinterpret_cast<uint2 *>(xq + (size_t)c * 8) = make_uint2(lo, hi);
-        if ((c & 3) == 0) {
-            const int kb = c >> 2;
-            sfb[(size_t)(kb >> 2) * kBsAtomBytes + (kb & 3)] = (uint8_t)min(max(ex + 127, 0), 255);
-        }
+        // 8 values = half of a 16-byte chunk of row t of the slab's tile; chunk cc sits at (cc ^ (t & 7))
+        const int slab = c >> 4, cc = (c >> 1) & 7, half = c & 1;
+        uint8_t *grp = xs + (size_t)(slab / p.sl) * group_bytes;
+        const int j = slab % p.sl;
+        *reinterpret_cast<uint2 *>(grp + j * kMoeBsXTile + t * 128 + ((cc ^ (t & 7)) << 4) + half * 8) = make_uint2(lo, hi);
+        if ((c & 3) == 0)
+            grp[p.sl * kMoeBsXTile + j * kBsAtomBytes + t * 16 + ((c >> 2) & 3)] = (uint8_t)min(max(ex + 127, 0), 255);
     }
 }
 
@@ -157,7 +164,6 @@ struct MoeBsRank {
 
 struct alignas(64) MoeBsParams {
     CUtensorMap tmap_w[WS_MAX_WORLD];  // expert slab as [e_len][n][k] 4-bit codes; boxes of 128 codes x tile_rows x 1, unpacked, 128B swizzle
-    CUtensorMap tmap_x[WS_MAX_WORLD];  // quantised activations [routes + 16][k bytes]; boxes of 128 bytes x 16 rows
     int32_t m, n, k, world;
     int32_t tile_rows, a_pitch, slabs_per_stage, nstages;
     int32_t tmem_cols, pad0;
@@ -172,12 +178,12 @@ struct MoeBsSmem {
 __host__ __device__ inline MoeBsSmem moe_bs_smem_layout(int nstages, int slabs_per_stage, int a_pitch, int m, int nslab_cta) {
     MoeBsSmem s{};
     const int nsl = nstages * slabs_per_stage;
-    const int b_bytes = nsl * kMoeBsCols * 128;
+    const int b_bytes = nsl * kMoeBsXSlab;  // per stage: its slabs' activation tiles, then their scale atoms (one bulk copy)
     int o = 0;
     s.a = o;    o += nsl * a_pitch;
     s.b = o;    o += b_bytes;
     if (b_bytes < kBsMmaRows * 128) o += kBsMmaRows * 128 - b_bytes;  // an MMA reads 128 rows behind the last weight slab
-    s.sf = o;   o += nsl * kBsAtomBytes;
+    s.sf = s.b;
     s.sfa = o;  o += 2 * nslab_cta * kBsAtomBytes;                      // weight-scale atoms of two passes
     s.acc = o;  o += m * kBsMmaRows * 4;                                // sums of (token, row)
     s.rx = o;   o += m * kBsMmaRows * 4;                                // the partner's, at the end
@@ -222,12 +228,13 @@ __global__ void __launch_bounds__(kMoeBsThreads, 1) moe_bs_kernel(const __grid_c
     const MoeBsWork W = moe_bs_work_layout(p.k);
     float *acc_s = reinterpret_cast<float *>(smem + S.acc);
     uint32_t *misc_s = reinterpret_cast<uint32_t *>(smem + S.misc);
-    const uint32_t a0 = smem_u32(smem + S.a), b0 = smem_u32(smem + S.b), sf0 = smem_u32(smem + S.sf), sfa0 = smem_u32(smem + S.sfa);
+    const uint32_t a0 = smem_u32(smem + S.a), b0 = smem_u32(smem + S.b), sfa0 = smem_u32(smem + S.sfa);
+    const uint32_t stage_x = (uint32_t)(SL * kMoeBsXSlab);  // a stage's activation tiles and scale atoms
     // full[s]: a stage's bytes landed; done[s]: its MMAs have completed (stage free); accfull[g] /
-    // accempty[g]: a pass's accumulator is complete / has been read; sfafull[b] / sfaempty[b]: the
-    // weight-scale atoms of a pass are written / have been copied into tensor memory.
+    // accempty[g]: a pass's accumulator is complete (and its scale columns free again) / has been read;
+    // sfafull[g]: the weight scales of a pass are in tensor memory.
     const uint32_t full0 = smem_u32(smem + S.bars), done0 = full0 + kMaxStages * 8;
-    const uint32_t accfull0 = done0 + kMaxStages * 8, accempty0 = accfull0 + 16, sfafull0 = accempty0 + 16, sfaempty0 = sfafull0 + 16;
+    const uint32_t accfull0 = done0 + kMaxStages * 8, accempty0 = accfull0 + 16, sfafull0 = accempty0 + 16;
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
@@ -237,8 +244,7 @@ __global__ void __launch_bounds__(kMoeBsThreads, 1) moe_bs_kernel(const __grid_c
         for (int b = 0; b < 2; ++b) {
             mbar_init(accfull0 + b * 8, 1);
             mbar_init(accempty0 + b * 8, 4);    // one arrival per epilogue warp
-            mbar_init(sfafull0 + b * 8, 128);   // every thread of the four scale warps
-            mbar_init(sfaempty0 + b * 8, 1);
+            mbar_init(sfafull0 + b * 8, 1);     // the commit that follows the scale warps' copies
         }
         mbar_fence_init();
     }
@@ -266,24 +272,20 @@ __global__ void __launch_bounds__(kMoeBsThreads, 1) moe_bs_kernel(const __grid_c
         // ------------------------------------------------------------ producer (one thread)
         if (lane == 0) {
             // the unpacking copy counts the packed bytes it read (64 per row), not the 128 it wrote
-            const uint32_t slab_tx = (uint32_t)(TR * 64 + kMoeBsCols * 128 + kBsAtomBytes);
+            const uint32_t slab_tx = (uint32_t)(TR * 64 + kMoeBsXSlab);
             RingPos st;
             int item = 0;
             for (int ps = 0; ps < npass; ++ps) {
                 const MoePass P = passes[ps];
-                const uint8_t *sfb = A.work + W.sfb + (size_t)ps * KS * kBsAtomBytes;
+                const uint8_t *xs = A.work + W.xs + ((size_t)ps * KS + k_lo) * kMoeBsXSlab;  // this CTA's slab groups of the pass
                 for (int i = 0; i < IP; ++i, ++item, st.next(NS)) {
                     const int s = st.s, j0 = i * SL, nsl = min(SL, NSLAB - j0);
                     if (item >= NS && !mbar_wait(done0 + s * 8, st.ph ^ 1u, X.status)) { ps = npass; break; }
                     mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)nsl * slab_tx);
-                    for (int j = 0; j < nsl; ++j) {
-                        const int slab = k_lo + j0 + j;
-                        tma_load_3d(a0 + (s * SL + j) * p.a_pitch, &p.tmap_w[vr], slab * 128, row0, (int)P.expert, full0 + s * 8);
-                        tma_load_2d(b0 + (s * SL + j) * (kMoeBsCols * 128), &p.tmap_x[vr], slab * 128, (int)P.first, full0 + s * 8);
-                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                     ::"r"(sf0 + (s * SL + j) * kBsAtomBytes), "l"(sfb + (size_t)slab * kBsAtomBytes),
-                                       "r"((uint32_t)kBsAtomBytes), "r"(full0 + s * 8) : "memory");
-                    }
+                    for (int j = 0; j < nsl; ++j)
+                        tma_load_3d(a0 + (s * SL + j) * p.a_pitch, &p.tmap_w[vr], (k_lo + j0 + j) * 128, row0, (int)P.expert, full0 + s * 8);
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(b0 + s * stage_x), "l"(xs + (size_t)i * stage_x), "r"(stage_x), "r"(full0 + s * 8) : "memory");
                 }
             }
         }
@@ -292,8 +294,8 @@ __global__ void __launch_bounds__(kMoeBsThreads, 1) moe_bs_kernel(const __grid_c
         if (lane == 0) {
             const uint32_t id0 = moe_bs_idesc(0), id1 = moe_bs_idesc(1), id2 = moe_bs_idesc(2), id3 = moe_bs_idesc(3);
             const uint32_t a_lo0 = umma_desc_lo(a0), b_lo0 = umma_desc_lo(b0);
-            const uint32_t a_step = (uint32_t)p.a_pitch >> 4, b_step = (uint32_t)(kMoeBsCols * 128) >> 4;
-            const uint64_t sf_desc0 = umma_desc(sf0, 128, false), sfa_desc0 = umma_desc(sfa0, 128, false);
+            const uint32_t a_step = (uint32_t)p.a_pitch >> 4, b_step = (uint32_t)kMoeBsXTile >> 4;
+            const uint64_t sf_desc0 = umma_desc(b0 + (uint32_t)(SL * kMoeBsXTile), 128, false);  // a stage's atoms follow its tiles
             const uint32_t sf_step = (uint32_t)kBsAtomBytes >> 4;
             RingPos st;
             bool ok = true;
@@ -304,51 +306,60 @@ __global__ void __launch_bounds__(kMoeBsThreads, 1) moe_bs_kernel(const __grid_c
                 tc_fence_after();
                 const uint32_t t_acc = tmem_base + (uint32_t)(g * kMoeBsCols);
                 uint32_t t_sc = t_sc0 + (uint32_t)(g * NSLAB * 8);
-                uint64_t sfa_desc = sfa_desc0 + (uint64_t)((uint32_t)(g * NSLAB) * sf_step);
                 bool first = true;
                 for (int i = 0; i < IP; ++i, st.next(NS)) {
                     const int s = st.s, nsl = min(SL, NSLAB - i * SL);
                     if (!mbar_wait(full0 + s * 8, st.ph, X.status)) { ok = false; break; }
                     tc_fence_after();
-                    uint32_t a_lo = a_lo0 + (uint32_t)(s * SL) * a_step, b_lo = b_lo0 + (uint32_t)(s * SL) * b_step;
-                    uint64_t sf_desc = sf_desc0 + (uint64_t)((uint32_t)(s * SL) * sf_step);
+                    uint32_t a_lo = a_lo0 + (uint32_t)(s * SL) * a_step, b_lo = b_lo0 + (uint32_t)s * (stage_x >> 4);
+                    uint64_t sf_desc = sf_desc0 + (uint64_t)((uint32_t)s * (stage_x >> 4));
                     for (int j = 0; j < nsl; ++j) {
-                        tmem_cp_atom(t_sc, sf_desc);          // the activations' scales of this slab
-                        tmem_cp_atom(t_sc + 4, sfa_desc);     // the weights'
+                        tmem_cp_atom(t_sc, sf_desc);          // the activations' scales of this slab (the weights' are there already)
                         if (first) umma_bs_ss<false>(t_acc, a_lo, b_lo, kUmmaDescHiSw128, kUmmaDescHiSw128, id0, t_sc + 4, t_sc);
                         else umma_bs_ss<true>(t_acc, a_lo, b_lo, kUmmaDescHiSw128, kUmmaDescHiSw128, id0, t_sc + 4, t_sc);
                         umma_bs_ss<true>(t_acc, a_lo + 2, b_lo + 2, kUmmaDescHiSw128, kUmmaDescHiSw128, id1, t_sc + 4, t_sc);
                         umma_bs_ss<true>(t_acc, a_lo + 4, b_lo + 4, kUmmaDescHiSw128, kUmmaDescHiSw128, id2, t_sc + 4, t_sc);
                         umma_bs_ss<true>(t_acc, a_lo + 6, b_lo + 6, kUmmaDescHiSw128, kUmmaDescHiSw128, id3, t_sc + 4, t_sc);
                         first = false;
-                        a_lo += a_step; b_lo += b_step; sf_desc += sf_step; sfa_desc += sf_step;
+                        a_lo += a_step; b_lo += b_step; sf_desc += sf_step;
                         t_sc += 8;
                     }
                     umma_commit(done0 + s * 8);  // the stage may be refilled
                 }
                 if (!ok) break;
-                umma_commit(sfaempty0 + g * 8);  // the weight-scale atoms have been copied
-                umma_commit(accfull0 + g * 8);   // the pass's sums are complete
+                umma_commit(accfull0 + g * 8);   // the pass's sums are complete; its scale columns may be rewritten
             }
         }
         __syncwarp();
     } else if (warp >= 6) {
-        // ------------------------------------------------------------ weight-scale atoms, one pass ahead
+        // ------------------------------------------------------------ weight scales, one pass ahead
+        // The expert's UE8M0 bytes of this CTA's rows and K half become scale atoms in shared memory
+        // (thread = row), and one thread copies them into the pass's tensor-memory columns: the
+        // MMA-issuing thread only waits for that commit.
         const int r = tid - 192;  // 0..127: row of the tile = lane of the atom
         const int row = row0 + r;
         const bool real = r < TR && row < p.n;
         const int kb32 = p.k >> 5;
+        const uint64_t sfa_desc0 = umma_desc(sfa0, 128, false);
         for (int ps = 0; ps < npass; ++ps) {
             const int g = ps & 1;
             const uint32_t lap = (uint32_t)(ps >> 1) & 1u;
-            if (ps >= 2 && !mbar_wait(sfaempty0 + g * 8, lap ^ 1u, X.status)) break;
+            // the pass that used these columns and this buffer last (ps - 2) has completed
+            if (ps >= 2 && !mbar_wait(accfull0 + g * 8, lap ^ 1u, X.status)) break;
             const int e = passes[ps].expert;
             uint8_t *dst = smem + S.sfa + (size_t)(g * NSLAB) * kBsAtomBytes + (r & 31) * 16 + (r >> 5) * 4;
             const uint32_t *src = reinterpret_cast<const uint32_t *>(A.s2 + ((size_t)e * p.n + (real ? row : 0)) * kb32) + k_lo;
             for (int j = 0; j < NSLAB; ++j)
                 *reinterpret_cast<uint32_t *>(dst + (size_t)j * kBsAtomBytes) = real ? __ldg(src + j) : 0x7F7F7F7Fu;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(sfafull0 + g * 8);
+            asm volatile("bar.sync 3, 128;" ::: "memory");
+            if (r == 0) {
+                tc_fence_after();
+                const uint32_t t_sfa = t_sc0 + (uint32_t)(g * NSLAB * 8) + 4u;
+                for (int j = 0; j < NSLAB; ++j)
+                    tmem_cp_atom(t_sfa + (uint32_t)(j * 8), sfa_desc0 + (uint64_t)((uint32_t)(g * NSLAB + j) * ((uint32_t)kBsAtomBytes >> 4)));
+                umma_commit(sfafull0 + g * 8);
+            }
         }
     } else {
         // ------------------------------------------------------------ epilogue warps 2-5
