@@ -418,7 +418,7 @@ def build_workload(wl: str, m: int, tp, synth, torch, dist, dev, sh, l2_bytes) -
         W.abytes = int(nw * per_expert + m * top_k * k * 2 + m * n * 4)
         W.h2d, W.d2h = m * top_k * k * 2, m * n * 4
         if world == 1 and m == 1:
-            W.captured_traffic = W.abytes * (47.12 / 46.79)
+            W.captured_traffic = W.abytes * (47.2 / 46.85)   # profiles/moe_bs_kernel_moe_down_m1.md
         return W
     raise SystemExit(f"unknown workload {wl}")
 
@@ -704,7 +704,7 @@ def main() -> None:
     ap.add_argument("--m", type=int, default=1, help="activation rows per step (1 = decode)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a graph replay")
     ap.add_argument("--no-others", action="store_true", help="skip the short measurements of the other fused steps")
-    ap.add_argument("--kernel", type=int, default=0, choices=[0, 1, 2],
+    ap.add_argument("--kernel", type=int, default=0, choices=[0, 1, 2, 3],
                     help="kernel choice as ws_tp_set_kernel takes it (0 = automatic, the default of the library)")
     ap.add_argument("--workload", default="o_proj", choices=["o_proj", "shared_down", "moe_down", "lm_head"],
                     help="o_proj is the headline step; the others are the path's remaining fused steps")
