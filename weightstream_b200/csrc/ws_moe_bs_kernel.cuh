@@ -253,6 +253,7 @@ __global__ void __launch_bounds__(kMoeBsThreads, 1) moe_bs_kernel(const __grid_c
         tmem_relinquish();
     }
     for (int i = tid; i < p.m * kBsMmaRows; i += kMoeBsThreads) acc_s[i] = 0.0f;
+    if (tid == 0) misc_s[8] = 0u;
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -344,8 +345,9 @@ __global__ void __launch_bounds__(kMoeBsThreads, 1) moe_bs_kernel(const __grid_c
         for (int ps = 0; ps < npass; ++ps) {
             const int g = ps & 1;
             const uint32_t lap = (uint32_t)(ps >> 1) & 1u;
-            // the pass that used these columns and this buffer last (ps - 2) has completed
-            if (ps >= 2 && !mbar_wait(accfull0 + g * 8, lap ^ 1u, X.status)) break;
+            // the pass that used these columns and this buffer last (ps - 2) has completed; a wait that
+            // gave up is told to all four warps at the barrier below, so that they leave the loop together
+            if (ps >= 2 && !mbar_wait(accfull0 + g * 8, lap ^ 1u, X.status)) misc_s[8] = 1u;
             const int e = passes[ps].expert;
             uint8_t *dst = smem + S.sfa + (size_t)(g * NSLAB) * kBsAtomBytes + (r & 31) * 16 + (r >> 5) * 4;
             const uint32_t *src = reinterpret_cast<const uint32_t *>(A.s2 + ((size_t)e * p.n + (real ? row : 0)) * kb32) + k_lo;
@@ -353,6 +355,7 @@ __global__ void __launch_bounds__(kMoeBsThreads, 1) moe_bs_kernel(const __grid_c
                 *reinterpret_cast<uint32_t *>(dst + (size_t)j * kBsAtomBytes) = real ? __ldg(src + j) : 0x7F7F7F7Fu;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("bar.sync 3, 128;" ::: "memory");
+            if (*reinterpret_cast<volatile uint32_t *>(misc_s + 8) != 0u) break;
             if (r == 0) {
                 tc_fence_after();
                 const uint32_t t_sfa = t_sc0 + (uint32_t)(g * NSLAB * 8) + 4u;
