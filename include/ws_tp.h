@@ -75,6 +75,17 @@ ws_status_t ws_tp_destroy(ws_tp_t *tp);
  * plane, crates/weightstream-transport/src/ctrl.rs:12-29). */
 ws_status_t ws_tp_export_handle(ws_tp_t *tp, ws_ipc_handle_t *out);
 ws_status_t ws_tp_connect_ipc(ws_tp_t *tp, const ws_ipc_handle_t *handles, int32_t n);
+/* The same exchange without a host framework: the ranks trade their handles over TCP (rank 0 listens on
+ * host:port, the others connect, retrying until timeout_ms has passed) and every rank connects as by
+ * ws_tp_connect_ipc.  Replaces, for this purpose, the reference's TCP control plane
+ * (crates/weightstream-transport/src/ctrl.rs:12-29, group bring-up in
+ * crates/weightstream-gpu/src/tp4.rs:191-312).  WS_ERR_TIMEOUT when a rank does not show up,
+ * WS_ERR_INVALID when a rank reports another world size, a rank number twice or one out of range. */
+ws_status_t ws_tp_connect_tcp(ws_tp_t *tp, int32_t rank, int32_t world, const char *host, int32_t port, int32_t timeout_ms);
+/* The rendezvous by itself (no device involved): every rank contributes `len` bytes and receives all
+ * ranks' bytes in rank order in `out` (world * len bytes). */
+ws_status_t ws_tcp_allgather(int32_t rank, int32_t world, const char *host, int32_t port, const void *in, void *out,
+                             int32_t len, int32_t timeout_ms);
 /* One process driving all ranks (several devices with peer access, or several
  * virtual ranks on one device for single-GPU testing). */
 ws_status_t ws_tp_connect_local(ws_tp_t *const *ranks, int32_t n);

@@ -112,6 +112,21 @@ def main():
         lm = O.fp8_gemv(wv, sv, F.bf16_bits_to_f32(xm), bn=128, bk=128, threads=4)
         assert [int(a) for a in am2.cpu()] == [O.argmax(lm[t]) for t in range(m)], f"argmax-only lm_head m={m}"
         assert same_everywhere(am2, world)
+    # a second endpoint brought up over the library's own TCP rendezvous (no torch.distributed involved
+    # in the handle exchange): the same o_proj step gives the same bits
+    ep2 = tp.Endpoint(sh, lr, max_m=16, max_n=7168, wait_ms=5000)
+    ep2.connect_tcp("127.0.0.1", int(os.environ.get("MASTER_PORT", "29500")) + 173, timeout_ms=20000)
+    xb = synth.activations_bf16(rng, 1, k)
+    k0, kl = sh.slice_of(k)
+    xd = torch.from_numpy(xb.view(np.int16)).to(dev).view(torch.bfloat16)[:, k0:k0 + kl].contiguous()
+    wd = torch.from_numpy(np.ascontiguousarray(w[:, k0:k0 + kl])).to(dev)
+    scd = torch.from_numpy(sc).to(dev)
+    o1 = ep.fp8_rowpar_gemm_allreduce(xd, wd, scd, k0=k0)
+    ep.check()
+    o2 = ep2.fp8_rowpar_gemm_allreduce(xd, wd, scd, k0=k0)
+    ep2.check()
+    assert torch.equal(o1.view(torch.int32), o2.view(torch.int32)), "endpoint connected over TCP differs"
+    ep2.close()
     ep.close()
     dist.barrier()
     if rank == 0:

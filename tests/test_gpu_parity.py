@@ -268,6 +268,26 @@ def test_collectives_bit_exact(dev, tpmod, oracle, world):
         grp.close()
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_allreduce_of_varying_lengths(dev, tpmod, oracle, world):
+    """The index-score all-reduce (engine.rs:3756-3775) sums a vector whose length changes from step to
+    step (the number of candidate positions): consecutive calls of different lengths on one endpoint,
+    from a single float to the endpoint's capacity, bit-exact with the rank-ordered fold."""
+    cap = 4100
+    grp = tpmod.LocalGroup(world, max_m=1, max_n=cap)
+    try:
+        for rnd, n in enumerate((1, 3, 255, 256, 1000, 4097, 2, cap, 33)):
+            ins = [gate_vector(rnd, r, n, world) for r in range(world)]
+            red = grp.allreduce([torch.from_numpy(v).to(dev) for v in ins])
+            grp.check()
+            want = oracle.allreduce_fold(np.stack(ins))
+            for r in range(world):
+                assert red[r].numel() == n
+                assert np.array_equal(red[r].cpu().numpy().view(np.uint32), want.view(np.uint32)), (n, r)
+    finally:
+        grp.close()
+
+
 def test_collectives_trait_tp1(dev, tpmod):
     """Collectives::allreduce / ::allgather on a world of one: host slice in, host vector out."""
     ep = tpmod.Endpoint(max_m=1, max_n=1024)

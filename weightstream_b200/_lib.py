@@ -23,6 +23,7 @@ STATUS_NAMES = {0: "WS_OK", -1: "WS_ERR_INVALID", -2: "WS_ERR_CUDA", -3: "WS_ERR
 # every symbol include/ws_tp.h declares
 EXPORTS = [
     "ws_tp_create", "ws_tp_destroy", "ws_tp_export_handle", "ws_tp_connect_ipc", "ws_tp_connect_local",
+    "ws_tp_connect_tcp", "ws_tcp_allgather",
     "ws_tp_check", "ws_tp_last_error", "ws_tp_stats", "ws_tp_num_ctas",
     "ws_fp8_rowpar_gemm_allreduce", "ws_fp8_rowpar_gemm_allreduce_group",
     "ws_moe_down_combine_allreduce", "ws_moe_down_combine_allreduce_group",
@@ -104,6 +105,10 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     L.ws_tp_export_handle.argtypes = [P, C.POINTER(IpcHandle)]
     L.ws_tp_connect_ipc.restype = st
     L.ws_tp_connect_ipc.argtypes = [P, C.POINTER(IpcHandle), C.c_int32]
+    L.ws_tp_connect_tcp.restype = st
+    L.ws_tp_connect_tcp.argtypes = [P, C.c_int32, C.c_int32, C.c_char_p, C.c_int32, C.c_int32]
+    L.ws_tcp_allgather.restype = st
+    L.ws_tcp_allgather.argtypes = [C.c_int32, C.c_int32, C.c_char_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]
     L.ws_tp_connect_local.restype = st
     L.ws_tp_connect_local.argtypes = [C.POINTER(P), C.c_int32]
     L.ws_tp_check.restype = st

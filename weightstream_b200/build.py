@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libws_tp.so")
-SOURCES = ["ws_api.cu"]
+SOURCES = ["ws_api.cu", "ws_bootstrap.cu"]
 HEADERS = ["ws_device.cuh", "ws_fp8_kernel.cuh", "ws_fp8_bs_kernel.cuh", "ws_moe_kernel.cuh", "ws_moe_gemv_kernel.cuh", "ws_moe_bs_kernel.cuh", "ws_misc_kernels.cuh",
            os.path.join("..", "..", "include", "ws_tp.h")]
 

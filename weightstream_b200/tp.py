@@ -207,6 +207,11 @@ class Endpoint:
         self.connect_ipc(got)  # type: ignore[arg-type]
         dist.barrier(group=group)
 
+    def connect_tcp(self, host: str, port: int, timeout_ms: int = 30000) -> None:
+        """One process per rank, no host framework: the ranks trade their IPC handles over TCP (rank 0
+        listens on host:port), as the reference's control plane does for its ring (ctrl.rs:12-29)."""
+        self._ok(self.lib.ws_tp_connect_tcp(self.handle, self.rank, self.world_size, host.encode(), int(port), int(timeout_ms)))
+
     def set_split(self, on: bool) -> None:
         self._ok(self.lib.ws_tp_set_split(self.handle, int(on)))
 
