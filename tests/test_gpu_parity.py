@@ -95,6 +95,7 @@ FP8_CASES = [
     (5120, 2304, "ue8m0", 32, 32, (1,)),         # reference shared-expert w2 (docs/model-spec.md)
     (7168, 2048, "f32", 128, 128, (1, 5)),       # shared-expert down at the measured shape
     (7168, 1024, "f32", 128, 128, (64, 37)),     # o_proj's K/8 shard: all 64 rows in one launch
+    (7168, 1024, "f32", 128, 128, (128, 100, 150)),  # 128 rows per launch (128 MMA columns); 150 = 128 + 22
 ]
 
 
@@ -193,7 +194,7 @@ def test_fp8_host_buffer_call_matches_device_call(dev, tpmod, oracle):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("n,k,m", [(512, 2048, 1), (7168, 8192, 1), (7168, 8192, 5), (1024, 1024, 19)])
+@pytest.mark.parametrize("n,k,m", [(512, 2048, 1), (7168, 8192, 1), (7168, 8192, 5), (1024, 1024, 19), (1024, 1024, 100)])
 @pytest.mark.parametrize("kernel", [0, 2, 1])
 def test_fp8_gemm_allreduce_virtual_ranks(dev, tpmod, oracle, world, n, k, m, kernel):
     """K sharded over `world` ranks (engine.rs:1477-1480); partials added in rank order
@@ -205,7 +206,7 @@ def test_fp8_gemm_allreduce_virtual_ranks(dev, tpmod, oracle, world, n, k, m, ke
     w, sc = synth.fp8_weight(rng, n, k)
     xb = synth.activations_bf16(rng, m, k)
     xf = F.bf16_bits_to_f32(xb)
-    grp = tpmod.LocalGroup(world, max_m=32, max_n=n)
+    grp = tpmod.LocalGroup(world, max_m=max(32, m), max_n=n)
     grp.set_kernel(kernel)
     try:
         wd, sd, xd = u8(w, dev), torch.from_numpy(sc).to(dev), bf16_tensor(xb, dev)

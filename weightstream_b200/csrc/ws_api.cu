@@ -298,7 +298,7 @@ ws_status_t ws_tp_create(int32_t world, int32_t rank, int32_t device, const ws_t
     if (set_smem(tp, moe_gemv_kernel) != WS_OK || set_smem(tp, fp8_rowpar_kernel<0>) != WS_OK || set_smem(tp, fp8_rowpar_kernel<1>) != WS_OK ||
         set_smem(tp, fp8_rowpar_kernel<2>) != WS_OK || set_smem(tp, moe_down_kernel) != WS_OK ||
         set_smem(tp, fp8_bs_kernel<16>) != WS_OK || set_smem(tp, fp8_bs_kernel<32>) != WS_OK ||
-        set_smem(tp, fp8_bs_kernel<64>) != WS_OK || set_smem(tp, moe_bs_kernel) != WS_OK ||
+        set_smem(tp, fp8_bs_kernel<64>) != WS_OK || set_smem(tp, fp8_bs_kernel<128>) != WS_OK || set_smem(tp, moe_bs_kernel) != WS_OK ||
         cudaFuncSetAttribute(moe_bs_prep_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
         // The prep kernel uses no shared memory, but a main-kernel CTA (which needs almost all of an SM's)
         // cannot move onto an SM whose L1/shared split must first change, and that has to wait for the prep
@@ -448,7 +448,7 @@ struct BsPlan {
 static BsPlan bs_plan(const ws_fp8_gemm_args_t &a, int mt, int skb, int ncta, bool pairs_allowed) {
     BsPlan u{};
     if (a.scale_kind != WS_SCALE_F32 || a.block_k % 128 || a.k % 128 || mt > kBsMaxTokens) return u;
-    u.mp = mt <= 16 ? 16 : mt <= 32 ? 32 : 64;
+    u.mp = mt <= 16 ? 16 : mt <= 32 ? 32 : mt <= 64 ? 64 : 128;
     // tiles of equal height that deal out evenly: a CTA's share of the rows, cut into as few pieces
     // of at most 128 rows as possible
     const int kslabs = a.k / 128;
@@ -564,7 +564,8 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
         q.r[i].ldx = a.ldx;
     }
     for (int i = 0; i < n; ++i) ranks[i]->step++;
-    void (*const kernel)(BsParams) = u.mp == 16 ? fp8_bs_kernel<16> : u.mp == 32 ? fp8_bs_kernel<32> : fp8_bs_kernel<64>;
+    void (*const kernel)(BsParams) = u.mp == 16 ? fp8_bs_kernel<16> : u.mp == 32 ? fp8_bs_kernel<32>
+                                     : u.mp == 64 ? fp8_bs_kernel<64> : fp8_bs_kernel<128>;
     const int prep_blocks = (int)(((int64_t)u.mp * (a0.k / 8) + 255) / 256);
     if (same_device) {
         WS_CUDA(t0, cudaSetDevice(t0->device));
@@ -828,7 +829,7 @@ static MoeBsPlan moe_bs_plan(const ws_moe_down_args_t &a, int ncta) {
     MoeBsPlan u{};
     u.ncta = ncta & ~1;
     const int nparts = u.ncta / 2, kslabs = a.k / 128;
-    if (nparts < 1 || a.k % 256 || kslabs / 2 > kMoeBsMaxSlabs || a.m > kBsMaxTokens) return u;
+    if (nparts < 1 || a.k % 256 || kslabs / 2 > kMoeBsMaxSlabs || a.m > 64) return u;  // 64 tokens: their sums fill 64 KB of shared memory
     u.tile_rows = (a.n + nparts - 1) / nparts;
     if (u.tile_rows > kBsMmaRows) return u;
     u.a_pitch = (u.tile_rows + 7) / 8 * 8 * 128;

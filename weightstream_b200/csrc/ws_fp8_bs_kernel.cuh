@@ -49,7 +49,7 @@ namespace ws {
 __host__ __device__ constexpr int bs_epi_warps(int mp) { return mp >= 64 ? 8 : 4; }
 __host__ __device__ constexpr int bs_threads(int mp) { return 64 + 32 * bs_epi_warps(mp); }
 constexpr int kBsMaxAcc = 8;         // accumulator groups in tensor memory (a group = one stage's slabs)
-constexpr int kBsMaxTokens = 64;     // activation rows one launch takes
+constexpr int kBsMaxTokens = 128;    // activation rows one launch takes (16, 32, 64 or 128 MMA columns)
 constexpr int kBsAtomBytes = 512;    // one scale atom: 128 rows x 4 K blocks
 constexpr int kBsMmaRows = 128;      // M of the MMA; a tile of output rows holds at most as many
 
