@@ -503,6 +503,10 @@ static BsPlan bs_plan(const ws_fp8_gemm_args_t &a, int mt, int skb, int ncta, bo
 static ws_status_t ensure_bs_scratch(ws_tp *tp, size_t bytes) {
     WS_CUDA(tp, cudaSetDevice(tp->device));
     if (bytes > tp->bs_work_bytes) {
+        // graphs of earlier host-buffer calls hold the old buffer's address: they go with it
+        for (auto &g : tp->hgraphs)
+            if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+        tp->hgraphs.clear();
         if (tp->bs_work) cudaFree(tp->bs_work);
         tp->bs_work = nullptr;
         tp->bs_work_bytes = 0;
