@@ -534,6 +534,8 @@ static ws_status_t bs_step(ws_tp *const *ranks, int n, const ws_fp8_gemm_args_t 
     p.slabs_per_stage = u.slabs_per_stage; p.nstages = u.nstages; p.nslot_max = u.nslot_max; p.skb = skb; p.nacc = u.nacc;
     p.csize = u.csize;
     p.tmem_cols = u.tmem_cols;
+    // 32 rows and more on four ranks and more: all-to-all of every partial sum costs more link time than the second hop
+    p.owner_reduce = (t0->world >= 4 && u.mp >= 32) ? 1 : 0;
     ncta = u.ncta;
     p.timeout_ns = t0->timeout_ns;
     p.lay = t0->lay;

@@ -99,7 +99,7 @@ struct alignas(64) BsParams {
     CUtensorMap tmap_x[WS_MAX_WORLD];  // quantised activations [mp][k bytes], box 128 bytes x mp, 128B swizzle
     int32_t m, mp, n, k, bn_shift, bk_shift;
     int32_t world, mode, vocab, tmem_cols;  // tmem_cols: tensor-memory columns to allocate (512, or at most 256 when two CTAs share an SM)
-    int32_t pad0;
+    int32_t owner_reduce;              // all-reduce by owners: tile t is folded by rank t % world, which sends the sums back
     int32_t csize;                     // 1, or 2: CTA pairs (a cluster) share a tile, each streams half of K
     int32_t tile_rows, ntiles;         // output rows per tile (<= 128) and tiles of the shard
     int32_t slabs_per_stage, nstages;
@@ -477,7 +477,9 @@ __global__ void __launch_bounds__(bs_threads(MP), 1) fp8_bs_kernel(const __grid_
                     for (int i = 0; i < CP; ++i)
                         if (col0 + i < p.m) A.out[(size_t)(col0 + i) * p.n + row] = v[i];
                 } else if (p.mode == kModeAllReduce) {
-                    for (int pr = 0; pr < p.world; ++pr) {
+                    // every rank gets the partial sums, or (many rows, many ranks) only the tile's owner
+                    const int pr0 = p.owner_reduce ? tile % p.world : 0, pr1 = p.owner_reduce ? pr0 + 1 : p.world;
+                    for (int pr = pr0; pr < pr1; ++pr) {
                         uint64_t *dst = reinterpret_cast<uint64_t *>(X.sym[pr] + p.lay.slota_off) + ((size_t)bank * p.world + X.rank) * astride;
 #pragma unroll
                         for (int i = 0; i < CP; ++i)
@@ -577,9 +579,14 @@ __global__ void __launch_bounds__(bs_threads(MP), 1) fp8_bs_kernel(const __grid_
                 // looked at (one memory round trip per batch, not per word); a word that has not
                 // arrived yet is then waited for on its own.  Ranks are added in rank order.
                 const int tend = min(p.m, col0 + CP);  // this thread's token columns
+                // Fold by owners: the sums of tile t are formed on rank t % world only (in rank order, as
+                // everywhere) and travel back in that rank's own slot at every peer, so all ranks end up
+                // with the same bits and each partial sum crosses the links once instead of world - 1 times.
+                const int owner = p.owner_reduce ? t % p.world : X.rank;
                 for (int tok0 = col0; tok0 < tend; tok0 += 16) {
                     float sum[16];
-                    for (int rr = 0; rr < p.world; ++rr) {
+                    const int rr0 = owner == X.rank ? 0 : owner, rr1 = owner == X.rank ? p.world : owner + 1;
+                    for (int rr = rr0; rr < rr1; ++rr) {
                         const uint64_t *src = slots + rr * astride + (size_t)tok0 * p.n + row;
                         uint64_t w[16];
 #pragma unroll
@@ -591,12 +598,21 @@ __global__ void __launch_bounds__(bs_threads(MP), 1) fp8_bs_kernel(const __grid_
                                 const float v = (uint32_t)(w[i] >> 32) == seq
                                                     ? __uint_as_float((uint32_t)w[i])
                                                     : wait_word(src + (size_t)i * p.n, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-                                sum[i] = rr == 0 ? v : sum[i] + v;
+                                sum[i] = rr == rr0 ? v : sum[i] + v;
                             }
                     }
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
                         if (tok0 + i < tend) A.out[(size_t)(tok0 + i) * p.n + row] = sum[i];
+                    if (p.owner_reduce && owner == X.rank)
+                        for (int pr = 0; pr < p.world; ++pr) {
+                            if (pr == X.rank) continue;
+                            uint64_t *dst = reinterpret_cast<uint64_t *>(X.sym[pr] + p.lay.slota_off) +
+                                            ((size_t)bank * p.world + X.rank) * astride + (size_t)tok0 * p.n + row;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (tok0 + i < tend) st_word_sys(dst + (size_t)i * p.n, seq, sum[i]);
+                        }
                 }
             }
         } else if (p.mode == kModeLmHead) {
