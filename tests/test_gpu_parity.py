@@ -350,7 +350,7 @@ def test_peer_that_ran_ahead_is_a_sequence_error(dev, tpmod):
 
 # ----------------------------------------------------------------------------- lm_head
 @pytest.mark.parametrize("world", [1, 2, 8])
-@pytest.mark.parametrize("m", [1, 2, 3, 20, 40])  # CUDA-core form (1, 2); tcgen05 kernel with 16, 32 and 64 token columns (3, 20, 40)
+@pytest.mark.parametrize("m", [1, 2, 3, 20, 40, 100])  # CUDA-core form (1, 2); tcgen05 kernel with 16, 32, 64 and 128 token columns
 @pytest.mark.parametrize("kernel", [0, 2, 1])
 def test_lm_head_small_vs_oracle(dev, tpmod, oracle, world, m, kernel):
     """Vocab-sharded head whose shards cut a 128-row scale block (as 129280/8 does): logits equal
@@ -362,7 +362,7 @@ def test_lm_head_small_vs_oracle(dev, tpmod, oracle, world, m, kernel):
     xb = synth.activations_bf16(rng, m, k)
     xf = F.bf16_bits_to_f32(xb)
     want = oracle.fp8_gemv(w, sc, xf, bn=128, bk=128, threads=oracle.max_threads())
-    grp = tpmod.LocalGroup(world, max_m=64, max_n=16, max_vocab=vocab)
+    grp = tpmod.LocalGroup(world, max_m=128, max_n=16, max_vocab=vocab)
     grp.set_kernel(kernel)
     try:
         wd, sd, xd = u8(w, dev), torch.from_numpy(sc).to(dev), bf16_tensor(xb, dev)
