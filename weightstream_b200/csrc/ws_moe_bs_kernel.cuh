@@ -173,7 +173,7 @@ struct alignas(64) MoeBsParams {
 };
 
 struct MoeBsSmem {
-    int32_t a, b, sf, sfa, acc, rx, bars, misc, total;
+    int32_t a, b, sfa, acc, rx, bars, misc, total;
 };
 __host__ __device__ inline MoeBsSmem moe_bs_smem_layout(int nstages, int slabs_per_stage, int a_pitch, int m, int nslab_cta) {
     MoeBsSmem s{};
@@ -183,7 +183,6 @@ __host__ __device__ inline MoeBsSmem moe_bs_smem_layout(int nstages, int slabs_p
     s.a = o;    o += nsl * a_pitch;
     s.b = o;    o += b_bytes;
     if (b_bytes < kBsMmaRows * 128) o += kBsMmaRows * 128 - b_bytes;  // an MMA reads 128 rows behind the last weight slab
-    s.sf = s.b;
     s.sfa = o;  o += 2 * nslab_cta * kBsAtomBytes;                      // weight-scale atoms of two passes
     s.acc = o;  o += m * kBsMmaRows * 4;                                // sums of (token, row)
     s.rx = o;   o += m * kBsMmaRows * 4;                                // the partner's, at the end
