@@ -337,6 +337,27 @@ __device__ __forceinline__ float wait_word(const uint64_t *p, uint32_t seq, uint
     }
 }
 
+// The ranks' words of one output, added in rank order.  All of them are requested before the first is
+// looked at, so that words that have already arrived cost one memory round trip together, not one each
+// (measured: eight dependent polls of local memory are ~5 us of an 8-rank step); a word that is not
+// there yet is then waited for on its own.
+__device__ __forceinline__ float fold_words(const uint64_t *slots, size_t astride, size_t off, int world, uint32_t seq,
+                                            uint64_t timeout_ns, uint32_t *status, uint32_t code) {
+    uint64_t w[WS_MAX_WORLD];
+#pragma unroll
+    for (int rr = 0; rr < WS_MAX_WORLD; ++rr)
+        if (rr < world) w[rr] = ld_word_sys(slots + (size_t)rr * astride + off);
+    float s = 0.0f;
+#pragma unroll
+    for (int rr = 0; rr < WS_MAX_WORLD; ++rr)
+        if (rr < world) {
+            const float v = (uint32_t)(w[rr] >> 32) == seq ? __uint_as_float((uint32_t)w[rr])
+                                                            : wait_word(slots + (size_t)rr * astride + off, seq, timeout_ns, status, code);
+            s = rr == 0 ? v : s + v;
+        }
+    return s;
+}
+
 // ---------------------------------------------------------------- step sequence
 // The step number that tags flags and selects the slot bank lives in device memory, so a
 // captured CUDA graph can be replayed: every CTA reads it when the kernel starts, and the last

@@ -547,10 +547,7 @@ __device__ __forceinline__ void fp8_rowpar_kernel_body(const Fp8Params &p) {
                                 (size_t)bank * p.world * astride;
         for_rows([&](int tok, int row, int) {
             const size_t off = (size_t)tok * p.n + row;
-            float s = wait_word(slots + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-            for (int rr = 1; rr < p.world; ++rr)
-                s += wait_word(slots + rr * astride + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-            A.out[off] = s;
+            A.out[off] = fold_words(slots, astride, off, p.world, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
         });
         return;
     }

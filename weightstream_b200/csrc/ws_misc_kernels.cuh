@@ -55,8 +55,7 @@ __device__ __forceinline__ void coll_body(const CollParams &p, const uint32_t se
         }
         const uint64_t *slots = reinterpret_cast<const uint64_t *>(X.sym[X.rank] + p.lay.slota_off) + (size_t)bank * p.world * astride;
         for (int64_t i = a + tid; i < b; i += blockDim.x) {
-            float s = wait_word(slots + i, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-            for (int r = 1; r < p.world; ++r) s += wait_word(slots + r * astride + i, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
+            const float s = fold_words(slots, astride, (size_t)i, p.world, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
             A.out[i] = s;
         }
         return;

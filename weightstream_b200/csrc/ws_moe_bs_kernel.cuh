@@ -424,9 +424,7 @@ __global__ void __launch_bounds__(kMoeBsThreads, 1) moe_bs_kernel(const __grid_c
                 const int tok = i >> 7, rc = i & 127, row = row0 + rc;
                 if (rc >= TR || row >= p.n) continue;
                 const size_t off = (size_t)tok * p.n + row;
-                float s = wait_word(slots + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-                for (int rr = 1; rr < p.world; ++rr) s += wait_word(slots + rr * astride + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-                A.out[off] = s;
+                A.out[off] = fold_words(slots, astride, off, p.world, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
             }
         }
     }

@@ -500,8 +500,7 @@ __device__ __forceinline__ void moe_gemv_body(const MoeGemvParams &p) {
     for (int i = tid; i < p.m * rows_cta; i += CT) {
         const int tok = i / rows_cta, r = i - tok * rows_cta;
         const size_t off = (size_t)tok * p.n + row_a + r;
-        float s = wait_word(slots + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
-        for (int rr = 1; rr < p.world; ++rr) s += wait_word(slots + rr * astride + off, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
+        const float s = fold_words(slots, astride, off, p.world, seq, p.timeout_ns, X.status, kStatTimeoutPeerA);
         A.out[off] = s;
     }
 }
