@@ -121,6 +121,15 @@ def _scale_kind(t: torch.Tensor) -> int:
     raise TypeError(f"scales must be uint8 (UE8M0) or fp32, got {t.dtype}")
 
 
+def _np_ptr(a: np.ndarray) -> int:
+    """Address of a numpy array's data; three times cheaper than ``a.ctypes.data`` (0.4 against 1.2 us),
+    which matters in a call that takes 35 us end to end."""
+    try:
+        return C.addressof(C.c_char.from_buffer(a))
+    except (TypeError, ValueError):  # read-only or empty buffers
+        return a.ctypes.data
+
+
 def _fp8_args(x, w, scales, block, row0, k0, out) -> Fp8GemmArgs:
     if x.dim() != 2 or w.dim() != 2 or scales.dim() != 2:
         raise ValueError("x, w and scales must be 2-D")
@@ -308,7 +317,7 @@ class Endpoint:
             hit = self._host_args[key] = (a, C.byref(a), w, scales)  # the tensors stay alive with their entry
         out = np.empty((m, n), dtype=np.float32)
         xh = x_host if x_host.flags["C_CONTIGUOUS"] else np.ascontiguousarray(x_host)
-        st = self._host_call(self.handle, hit[1], xh.ctypes.data, out.ctypes.data)
+        st = self._host_call(self.handle, hit[1], _np_ptr(xh), _np_ptr(out))
         if st != WS_OK:
             self._ok(st)
         return out
