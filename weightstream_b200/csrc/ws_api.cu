@@ -608,6 +608,8 @@ static bool bs_wanted(const ws_tp *t0, int mt, const ws_fp8_gemm_args_t &a, bool
     if (t0->kernel_sel == 2) return true;
     if (t0->kernel_sel != 0) return false;
     // an argmax-only lm_head step also saves the exchange of one candidate per CTA (this kernel sends one per rank)
+    // two rows: the CUDA-core kernel needs 23 us for a 58.7 MB shard, this one 17.8 (it is the same for 2 to 8 rows)
+    if (mt == 2 && (int64_t)a.n * a.k >= ((int64_t)32 << 20)) return true;
     return mt >= 3 || (int64_t)a.n * a.k >= ((int64_t)(lm_head ? 32 : 128) << 20);
 }
 
